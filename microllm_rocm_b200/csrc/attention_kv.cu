@@ -1,7 +1,8 @@
 // Softmax attention whose keys and values may have different widths, with the steps that come between the
 // projections and the scores:
 //
-//   mlb_qk_prepare          per head: rms norm of q and k with a shared weight (optional), rotation of the first `rot_dims`
+//   mlb_qk_prepare          per head: rms norm of q and k, each with a weight shared by the heads or with none (optional;
+//                           `norm_where` 1: in front of the rotation, 2: behind it), rotation of the first `rot_dims`
 //                           elements in interleaved pairs (2i, 2i + 1) by position * freq[i] with cos and sin times
 //                           `magnitude` (optional), q times 1 + coef * ln(floor((pos + 1) / every) + 1) (optional);
 //                           q goes out in the compute dtype, k and v into the pages.  v may be the projected k itself.
@@ -39,6 +40,7 @@ struct PrepareParams {
     Columns q, k, v;           // q: H * DK columns from q_col, k: G * DK, v: G * DV (v may alias k's columns)
     int q_col, k_col, v_col;
     const float* q_norm; const float* k_norm; float eps;
+    int norm_where;            // 0: no norm, 1: before the rotation, 2: after it (a null weight: the plain quotient)
     const float* freq; int rot_dims; float magnitude;
     float temp_coef; int temp_every;
     const int* positions; const int* token_seq; const int* block_table;
@@ -89,19 +91,20 @@ __global__ void __launch_bounds__(WARPS * 32) qk_prepare_kernel(PrepareParams p)
                                    : (size_t)p.G * p.page_size * p.PK + ((size_t)head * p.page_size + pos % p.page_size) * p.PV;
         page_row = (KVT*)p.pages + (size_t)page * page_stride + within;
     }
-    float ss = 0.0f;
-#pragma unroll
-    for (int i = 0; i < NL; ++i) ss = fmaf(x[i], x[i], ss);
     if (is_q || is_k) {
         const float* w = is_q ? p.q_norm : p.k_norm;
-        if (w) {
+        auto norm = [&]() {
+            float ss = 0.0f;
+#pragma unroll
+            for (int i = 0; i < NL; ++i) ss = fmaf(x[i], x[i], ss);
             const float inv = 1.0f / sqrtf(warp_sum(ss) / (float)D + p.eps);
 #pragma unroll
             for (int i = 0; i < NL; ++i) {
                 const int c = lane + 32 * i;
-                if (c < D) x[i] = x[i] * inv * w[c];
+                if (c < D) x[i] = w ? x[i] * inv * w[c] : x[i] * inv;
             }
-        }
+        };
+        if (p.norm_where == 1) norm();
         if (p.freq && p.rot_dims > 0) {
 #pragma unroll
             for (int i = 0; i < NL; ++i) {
@@ -114,6 +117,7 @@ __global__ void __launch_bounds__(WARPS * 32) qk_prepare_kernel(PrepareParams p)
                 }
             }
         }
+        if (p.norm_where == 2) norm();
         if (is_q && p.temp_every > 0) {
             const float temp = 1.0f + p.temp_coef * logf((float)((pos + 1) / p.temp_every) + 1.0f);
 #pragma unroll
@@ -137,6 +141,7 @@ struct AttnParams {
     const int* positions; const int* token_seq; const int* block_table;
     int max_blocks, num_pages, page_size;
     int tokens, num_heads, num_kv_heads, dk, dv;
+    int chunk;               // > 0: only keys of the query's own block of `chunk` positions (counted from 0)
     int window;              // 0: all earlier keys
     float scale;
     Columns gate; int gate_col;      // gate.base null: no gate
@@ -155,7 +160,7 @@ __global__ void __launch_bounds__(WARPS * 32) paged_attention_kv_kernel(AttnPara
     const int kvh = h / (p.num_heads / p.num_kv_heads);
     const int pos = p.positions[t];
     const int seq = p.token_seq[t];
-    const int lo = (p.window > 0 && pos - p.window + 1 > 0) ? pos - p.window + 1 : 0;
+    const int lo = first_visible_key(pos, p.window, p.chunk);
 
     const QT* qrow = (const QT*)p.q + ((size_t)t * p.num_heads + h) * DK;
     for (int c = lane; c < DK; c += 32) q_s[warp][c] = to_f32(qrow[c]);
@@ -268,7 +273,7 @@ MLB_EXPORT int mlb_gate_heads(const void* o, void* out, int dtype, const float* 
 
 MLB_EXPORT int mlb_qk_prepare(const float* src, long long ld, int n_partials, long long partial_stride, int q_col, int k_col,
                               int v_col, const float* kv_src, long long kv_ld, int kv_partials, long long kv_partial_stride,
-                              const float* q_norm, const float* k_norm, float eps, const float* freq, int rot_dims,
+                              const float* q_norm, const float* k_norm, float eps, int norm_where, const float* freq, int rot_dims,
                               float magnitude, float temp_coef, int temp_every, const int* positions, const int* token_seq,
                               const int* block_table, int max_blocks, int num_pages, int page_size, void* q_out, int q_dtype,
                               void* pages, int kv_dtype, int T, int H, int G, int DK, int DV, int stored_k, int stored_v,
@@ -279,6 +284,7 @@ MLB_EXPORT int mlb_qk_prepare(const float* src, long long ld, int n_partials, lo
         return fail(MLB_UNSUPPORTED_SIZE, "qk_prepare: heads %d/%d, widths %d/%d (at most %d)", H, G, DK, DV, MAX_D);
     if (stored_k < DK || stored_v < DV || stored_k > MAX_D || stored_v > MAX_D)
         return fail(MLB_INVALID_ARGUMENT, "qk_prepare: stored widths %d/%d for %d/%d (at most %d)", stored_k, stored_v, DK, DV, MAX_D);
+    if (norm_where < 0 || norm_where > 2) return fail(MLB_INVALID_ARGUMENT, "qk_prepare: norm_where %d", norm_where);
     if (rot_dims < 0 || rot_dims % 2 || rot_dims > DK) return fail(MLB_INVALID_ARGUMENT, "qk_prepare: rot_dims %d of %d", rot_dims, DK);
     if (pages && (page_size <= 0 || num_pages <= 0 || max_blocks <= 0 || !block_table))
         return fail(MLB_INVALID_ARGUMENT, "qk_prepare: bad cache geometry");
@@ -287,7 +293,7 @@ MLB_EXPORT int mlb_qk_prepare(const float* src, long long ld, int n_partials, lo
     p.q = Columns{src, ld, n_partials, partial_stride};
     p.k = p.v = kv_src ? Columns{kv_src, kv_ld, kv_partials, kv_partial_stride} : p.q;
     p.q_col = q_col; p.k_col = k_col; p.v_col = v_col;
-    p.q_norm = q_norm; p.k_norm = k_norm; p.eps = eps; p.freq = freq; p.rot_dims = rot_dims; p.magnitude = magnitude;
+    p.q_norm = q_norm; p.k_norm = k_norm; p.eps = eps; p.norm_where = norm_where; p.freq = freq; p.rot_dims = rot_dims; p.magnitude = magnitude;
     p.temp_coef = temp_coef; p.temp_every = temp_every; p.positions = positions; p.token_seq = token_seq; p.block_table = block_table;
     p.max_blocks = max_blocks; p.num_pages = num_pages; p.page_size = page_size; p.q_out = q_out; p.pages = pages;
     p.T = T; p.H = H; p.G = G; p.DK = DK; p.DV = DV; p.PK = stored_k; p.PV = stored_v; p.error_flag = error_flag;
@@ -315,17 +321,17 @@ MLB_EXPORT int mlb_qk_prepare(const float* src, long long ld, int n_partials, lo
 MLB_EXPORT int mlb_paged_attention_kv(const void* q, int q_dtype, const void* pages, int kv_dtype, void* out, int out_dtype,
                                       const int* positions, const int* token_seq, const int* block_table, int max_blocks,
                                       int num_pages, int page_size, int tokens, int num_heads, int num_kv_heads, int dk, int dv,
-                                      int window, float scale, const float* gate, long long gate_ld, int gate_partials,
+                                      int window, int chunk, float scale, const float* gate, long long gate_ld, int gate_partials,
                                       long long gate_partial_stride, int gate_col, int* error_flag, cudaStream_t stream) {
     if (tokens < 0 || num_heads <= 0 || num_kv_heads <= 0 || num_heads % num_kv_heads != 0)
         return fail(MLB_INVALID_ARGUMENT, "paged_attention_kv: bad head counts %d/%d", num_heads, num_kv_heads);
     if (dk <= 0 || dk > MAX_D || dv <= 0 || dv > MAX_D)
         return fail(MLB_UNSUPPORTED_SIZE, "paged_attention_kv: widths %d/%d not in 1..%d", dk, dv, MAX_D);
-    if (page_size <= 0 || num_pages <= 0 || max_blocks <= 0 || window < 0)
+    if (page_size <= 0 || num_pages <= 0 || max_blocks <= 0 || window < 0 || chunk < 0)
         return fail(MLB_INVALID_ARGUMENT, "paged_attention_kv: bad cache geometry");
     if (tokens == 0) return MLB_OK;
     AttnParams p{q, pages, out, positions, token_seq, block_table, max_blocks, num_pages, page_size, tokens, num_heads,
-                 num_kv_heads, dk, dv, window, scale, Columns{gate, gate_ld, gate_partials < 1 ? 1 : gate_partials, gate_partial_stride},
+                 num_kv_heads, dk, dv, chunk, window, scale, Columns{gate, gate_ld, gate_partials < 1 ? 1 : gate_partials, gate_partial_stride},
                  gate_col, error_flag};
     const long long items = (long long)tokens * num_heads;
     const unsigned blocks = (unsigned)((items + WARPS - 1) / WARPS);

@@ -60,6 +60,7 @@ struct FaParams {
     const int* work;                // [num_work, 2] (sequence, first row tile)
     int max_blocks, num_pages, page_size;
     int num_heads, num_kv_heads, group;
+    int chunk;               // > 0: only keys of the query's own block of `chunk` positions (counted from 0)
     int window;
     float scale_log2;               // softmax scale * log2(e)
     int page_shift;                 // log2(page_size) when it is a power of two, else -1
@@ -306,7 +307,7 @@ __device__ __forceinline__ void attend(const FaParams& p, const TileGeometry& ge
         const int tok = geo.token_of(g + 8 * i, p.group);
         if (tok < geo.n_new) {
             pos_row[i] = geo.pos0 + tok;
-            lo_row[i] = (p.window > 0 && pos_row[i] - p.window + 1 > 0) ? pos_row[i] - p.window + 1 : 0;
+            lo_row[i] = first_visible_key(pos_row[i], p.window, p.chunk);
         } else {
             pos_row[i] = -1;            // padding row: sees nothing
             lo_row[i] = 0;
@@ -449,7 +450,7 @@ __global__ void __launch_bounds__(WARPS * 32, 2) fa_prefill_kernel(FaParams p) {
     // key range of the whole CTA (first row's window start .. last row's position)
     const int cta_row_first = first_tile * 16, cta_row_last = min(total_rows, cta_row_first + WARPS * 16) - 1;
     const int cta_first_pos = geo.pos0 + cta_row_first / p.group, cta_last_pos = geo.pos0 + cta_row_last / p.group;
-    const int cta_lo = (p.window > 0 && cta_first_pos - p.window + 1 > 0) ? cta_first_pos - p.window + 1 : 0;
+    const int cta_lo = first_visible_key(cta_first_pos, p.window, p.chunk);
     const int tile_first = cta_lo / KEY_TILE, tile_last = cta_last_pos / KEY_TILE;
 
     PageTable pt;
@@ -483,7 +484,7 @@ __global__ void __launch_bounds__(WARPS * 32, 2) fa_prefill_kernel(FaParams p) {
         const int tok = geo.token_of(g + 8 * i, p.group);
         if (active && tok < geo.n_new) {
             pos_row[i] = geo.pos0 + tok;
-            lo_row[i] = (p.window > 0 && pos_row[i] - p.window + 1 > 0) ? pos_row[i] - p.window + 1 : 0;
+            lo_row[i] = first_visible_key(pos_row[i], p.window, p.chunk);
         } else {
             pos_row[i] = -1;
             lo_row[i] = 0;
@@ -492,8 +493,8 @@ __global__ void __launch_bounds__(WARPS * 32, 2) fa_prefill_kernel(FaParams p) {
     // the warp's own key range: tiles outside it are skipped (it still keeps step with the CTA)
     const int warp_first_pos = geo.pos0 + geo.token_of(0, p.group);
     const int warp_last_pos = geo.pos0 + min(geo.token_of(15, p.group), geo.n_new - 1);
-    const int warp_lo = (p.window > 0 && warp_first_pos - p.window + 1 > 0) ? warp_first_pos - p.window + 1 : 0;
-    const int warp_lo_last = (p.window > 0 && warp_last_pos - p.window + 1 > 0) ? warp_last_pos - p.window + 1 : 0;
+    const int warp_lo = first_visible_key(warp_first_pos, p.window, p.chunk);
+    const int warp_lo_last = first_visible_key(warp_last_pos, p.window, p.chunk);
     const bool warp_rows_full = geo.row0 + 16 <= total_rows;
 
     // lane-constant parts of the swizzled ldmatrix addresses (row & 7 is the lane's low bits)
@@ -695,7 +696,7 @@ __global__ void __launch_bounds__(DW * 32, DW == 4 ? 2 : 1) fa_decode_kernel(FaP
                     threadIdx.x, DW * 32);
     geo.pos0 = pos0_load;
     const int last_pos = geo.pos0;
-    const int lo = (p.window > 0 && last_pos - p.window + 1 > 0) ? last_pos - p.window + 1 : 0;
+    const int lo = first_visible_key(last_pos, p.window, p.chunk);
     int tile_begin = lo / 16, tile_end = last_pos / 16 + 1;
     const int splits = (int)gridDim.z, rank = (int)blockIdx.z;
     if (splits > 1) {                        // this CTA's even share of the sequence's key tiles
@@ -1040,7 +1041,7 @@ __global__ void __launch_bounds__(DW * 32, DW == 4 ? 2 : 1) fa_decode_t_kernel(F
                     threadIdx.x, DW * 32);
     geo.pos0 = pos0_load;
     const int last_pos = geo.pos0;
-    const int lo = (p.window > 0 && last_pos - p.window + 1 > 0) ? last_pos - p.window + 1 : 0;
+    const int lo = first_visible_key(last_pos, p.window, p.chunk);
     int tile_begin = lo / 16, tile_end = last_pos / 16 + 1;
     const int splits = (int)gridDim.z, rank = (int)blockIdx.z;
     if (splits > 1) {                        // this CTA's even share of the sequence's key tiles
@@ -1220,7 +1221,7 @@ __global__ void __launch_bounds__(160, 2) fa_decode_ring_kernel(const __grid_con
     }
     geo.pos0 = pos0_load;
     const int last_pos = geo.pos0;
-    const int lo = (p.window > 0 && last_pos - p.window + 1 > 0) ? last_pos - p.window + 1 : 0;
+    const int lo = first_visible_key(last_pos, p.window, p.chunk);
     int tile_begin = lo / 16, tile_end = last_pos / 16 + 1;
     const int splits = (int)gridDim.z, rank = (int)blockIdx.z;
     if (splits > 1) {                        // this CTA's even share of the sequence's key tiles
@@ -1385,13 +1386,13 @@ MLB_EXPORT int mlb_fa_max_splits() { return MAX_SPLITS; }
 MLB_EXPORT int mlb_paged_attention_mma(const void* q, const void* pages, void* out, const int* seq_starts,
                                        const int* seq_pos0, const int* block_table, const int* work, int num_work,
                                        int max_blocks, int num_pages, int page_size, int num_heads, int num_kv_heads,
-                                       int window, float scale, int mode, int splits, int* error_flag,
+                                       int window, int chunk, float scale, int mode, int splits, int* error_flag,
                                        cudaStream_t stream) {
     if (num_heads <= 0 || num_kv_heads <= 0 || num_heads % num_kv_heads != 0)
         return fail(MLB_INVALID_ARGUMENT, "paged_attention_mma: bad head counts %d/%d", num_heads, num_kv_heads);
     if (page_size <= 0 || page_size % 16 != 0)
         return fail(MLB_UNSUPPORTED_SIZE, "paged_attention_mma: page_size %d must be a multiple of 16", page_size);
-    if (num_pages <= 0 || max_blocks <= 0 || window < 0 || num_work < 0)
+    if (num_pages <= 0 || max_blocks <= 0 || window < 0 || chunk < 0 || num_work < 0)
         return fail(MLB_INVALID_ARGUMENT, "paged_attention_mma: bad cache geometry");
     const bool force_ring = (mode & 4) != 0, forbid_ring = (mode & 8) != 0;
     mode &= 3;
@@ -1404,7 +1405,7 @@ MLB_EXPORT int mlb_paged_attention_mma(const void* q, const void* pages, void* o
     if (num_work == 0) return MLB_OK;
     FaParams p{(const __nv_bfloat16*)q, (const __nv_bfloat16*)pages, (__nv_bfloat16*)out, seq_starts, seq_pos0,
                block_table, work, max_blocks, num_pages, page_size, num_heads, num_kv_heads,
-               num_heads / num_kv_heads, window, scale * LOG2E, (page_size & (page_size - 1)) == 0 ? __builtin_ctz((unsigned)page_size) : -1, error_flag,
+               num_heads / num_kv_heads, chunk, window, scale * LOG2E, (page_size & (page_size - 1)) == 0 ? __builtin_ctz((unsigned)page_size) : -1, error_flag,
                mode == 2 ? 1 : 0};
     if (mode == 0) {
         static bool prefill_configured_on[MAX_DEVICES] = {false};

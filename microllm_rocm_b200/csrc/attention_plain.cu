@@ -34,6 +34,7 @@ struct AttnParams {
     const int* block_table;  // [A, max_blocks]
     int max_blocks, num_pages, page_size;
     int tokens, num_heads, num_kv_heads, head_dim;
+    int chunk;               // > 0: only keys of the query's own block of `chunk` positions (counted from 0)
     int window;              // 0: all earlier keys
     float scale;
     int* error_flag;
@@ -52,7 +53,7 @@ paged_attention_plain_kernel(AttnParams p) {
     const int kvh = h / (p.num_heads / p.num_kv_heads);
     const int pos = p.positions[t];
     const int seq = p.token_seq[t];
-    const int lo = (p.window > 0 && pos - p.window + 1 > 0) ? pos - p.window + 1 : 0;
+    const int lo = first_visible_key(pos, p.window, p.chunk);
 
     const QT* qrow = (const QT*)p.q + ((size_t)t * p.num_heads + h) * D;
     for (int c = lane; c < D; c += 32) q_s[warp][c] = to_f32(qrow[c]);
@@ -123,17 +124,17 @@ paged_attention_plain_kernel(AttnParams p) {
 MLB_EXPORT int mlb_paged_attention_plain(const void* q, int q_dtype, const void* pages, int kv_dtype, void* out,
                                          int out_dtype, const int* positions, const int* token_seq,
                                          const int* block_table, int max_blocks, int num_pages, int page_size,
-                                         int tokens, int num_heads, int num_kv_heads, int head_dim, int window,
+                                         int tokens, int num_heads, int num_kv_heads, int head_dim, int window, int chunk,
                                          float scale, int* error_flag, cudaStream_t stream) {
     if (tokens < 0 || num_heads <= 0 || num_kv_heads <= 0 || num_heads % num_kv_heads != 0)
         return fail(MLB_INVALID_ARGUMENT, "paged_attention_plain: bad head counts %d/%d", num_heads, num_kv_heads);
     if (head_dim <= 0 || head_dim > MAX_D)
         return fail(MLB_UNSUPPORTED_SIZE, "paged_attention_plain: head_dim %d not in 1..%d", head_dim, MAX_D);
-    if (page_size <= 0 || num_pages <= 0 || max_blocks <= 0 || window < 0)
+    if (page_size <= 0 || num_pages <= 0 || max_blocks <= 0 || window < 0 || chunk < 0)
         return fail(MLB_INVALID_ARGUMENT, "paged_attention_plain: bad cache geometry");
     if (tokens == 0) return MLB_OK;
     AttnParams p{q, pages, out, positions, token_seq, block_table, max_blocks, num_pages, page_size,
-                 tokens, num_heads, num_kv_heads, head_dim, window, scale, error_flag};
+                 tokens, num_heads, num_kv_heads, head_dim, chunk, window, scale, error_flag};
     const long long items = (long long)tokens * num_heads;
     const unsigned blocks = (unsigned)((items + WARPS - 1) / WARPS);
     if (q_dtype == MLB_F32 && kv_dtype == MLB_F32 && out_dtype == MLB_F32)

@@ -74,7 +74,7 @@ struct TcParams {
     const int* block_table;         // [A, max_blocks]
     const int* work;                // [num_work, 2] (sequence, 128-row tile of its new tokens)
     int max_blocks, num_pages, page_size, pages_per_tile;
-    int num_heads, num_kv_heads, group, window;
+    int num_heads, num_kv_heads, group, window, chunk;
     float scale_log2;
     int* error_flag;
 };
@@ -243,7 +243,7 @@ fa_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
     const int row_first = q_tile * BM;
     const int rows = min(BM, n_new - row_first);
     const int qpos_first = pos0 + row_first, qpos_last = qpos_first + rows - 1;
-    const int lo = (p.window > 0 && qpos_first - p.window + 1 > 0) ? qpos_first - p.window + 1 : 0;
+    const int lo = first_visible_key(qpos_first, p.window, p.chunk);
     const int kt_begin = lo / BN;
     const int n_tiles = qpos_last / BN + 1 - kt_begin;
     const int kvh = head / p.group;
@@ -370,7 +370,7 @@ fa_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
         const int r = quarter * 32 + lane;
         const uint32_t lane_base = tmem_base + ((uint32_t)(quarter * 32) << 16);
         const int qpos = qpos_first + r;
-        const int lo_r = p.window > 0 ? qpos - p.window + 1 : -0x40000000;
+        const int lo_r = first_visible_key(qpos, p.window, p.chunk);
         float m_used = -INFINITY, l = 0.0f;
         bool ok = true;
         // the tensor-memory instructions below are warp-wide: a wait gives up for the whole warp or not at all
@@ -392,7 +392,7 @@ fa_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
             if (lane == 0) mbar_arrive(smem_u32(&s_empty[buf]));
 
             const int kbase = (kt_begin + j) * BN;
-            const bool edge = (kbase + BN - 1 > qpos_first) || (p.window > 0 && kbase < qpos_last - p.window + 1);
+            const bool edge = (kbase + BN - 1 > qpos_first) || (kbase < first_visible_key(qpos_last, p.window, p.chunk));
             float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};       // four chains: no 128-long dependence
             if (edge) {
 #pragma unroll
@@ -558,11 +558,11 @@ MLB_EXPORT int mlb_fa_tc_supported(int page_size, float scale) {
 MLB_EXPORT int mlb_paged_attention_tc(const void* q, long long ldq, const void* pages, void* out, long long ldo, int tokens,
                                       const int* seq_starts, const int* seq_pos0, const int* block_table, const int* work,
                                       int num_work, int max_blocks, int num_pages, int page_size, int num_heads,
-                                      int num_kv_heads, int window, float scale, int* error_flag, cudaStream_t stream) {
+                                      int num_kv_heads, int window, int chunk, float scale, int* error_flag, cudaStream_t stream) {
     if (num_heads <= 0 || num_kv_heads <= 0 || num_heads % num_kv_heads != 0)
         return fail(MLB_INVALID_ARGUMENT, "attention_tc: bad head counts %d/%d", num_heads, num_kv_heads);
     if (!mlb_fa_tc_supported(page_size, scale)) return MLB_UNSUPPORTED_SIZE;
-    if (num_pages <= 0 || max_blocks <= 0 || window < 0 || num_work < 0 || tokens < 0)
+    if (num_pages <= 0 || max_blocks <= 0 || window < 0 || chunk < 0 || num_work < 0 || tokens < 0)
         return fail(MLB_INVALID_ARGUMENT, "attention_tc: bad cache geometry");
     if (ldq < (long long)num_heads * D || ldo < (long long)num_heads * D || ldq % 8 != 0 || ldo % 8 != 0 ||
         ((uintptr_t)q & 15) || ((uintptr_t)out & 15) || ((uintptr_t)pages & 15))
@@ -579,7 +579,7 @@ MLB_EXPORT int mlb_paged_attention_tc(const void* q, long long ldq, const void* 
     if (status != MLB_OK) return status;
 
     TcParams p{(__nv_bfloat16*)out, ldo, seq_starts, seq_pos0, block_table, work, max_blocks, num_pages, page_size,
-               BN / page_size, num_heads, num_kv_heads, num_heads / num_kv_heads, window, scale * LOG2E, error_flag};
+               BN / page_size, num_heads, num_kv_heads, num_heads / num_kv_heads, window, chunk, scale * LOG2E, error_flag};
     static bool configured_on[MAX_DEVICES] = {false};         // the attribute belongs to the device
     bool& configured = configured_on[device_index()];
     if (!configured) {

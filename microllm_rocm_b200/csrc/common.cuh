@@ -84,6 +84,14 @@ template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(flo
 }                                    // float_to_bfloat16_bits (base/low_precision.h:69-74)
 
 // ---- reductions with a fixed order (the result never depends on the batch) ------------
+// The first key a query at position `pos` may see: the start of its window of `window` keys (itself included; 0: no
+// window) or of its own block of `chunk` positions counted from 0 (0: no blocks), whichever is later.  Both grow with pos.
+__device__ __forceinline__ int first_visible_key(int pos, int window, int chunk) {
+    int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+    if (chunk > 0 && pos > 0) { const int c = pos - pos % chunk; if (c > lo) lo = c; }
+    return lo;
+}
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

@@ -11,6 +11,10 @@
 //                       head), eight or sixteen lanes share a column's DK rows in registers and meet by shuffles twice a token.
 //   mlb_delta_output    o / rms(o) per head * weight * sigmoid(W2g a_g), stored in the compute dtype.
 //
+// The scan kernel also runs the two simpler recurrences with a decay per key channel (mlb_linear_scan, `rule`):
+//   rule 1, decayed sum:   S <- diag(g_t) S + k_t v_t^T;   o_t = S^T q_t
+//   rule 2, bonus read:    o_t = (S + diag(u) k_t v_t^T)^T q_t;   then S <- diag(g_t) S + k_t v_t^T      (u [H, DK], fixed)
+//
 // The order of every addition depends on the token's place in its sequence only, never on how the sequence was cut
 // into steps: a token's result is the same bits however it is scheduled.
 #include "common.cuh"
@@ -103,7 +107,8 @@ __global__ void __launch_bounds__(WARPS * 32) delta_prepare_kernel(PrepareParams
 struct ScanParams {
     const float* qn; const float* kn;        // [T, G * DK]
     const float* g;                          // [T, H * DK]
-    const float* beta;                       // [T, H]
+    const float* beta;                       // [T, H] (the delta rule only; else unused and may be null)
+    const float* bonus;                      // [H, DK] (rule 2 only)
     const float* v; long long ld_v;          // [T, H * DV] (a column block of the convolved rows)
     float* o;                                // [T, H * DV]
     float* state;                            // [slots + 1, H, DK, DV]
@@ -135,7 +140,9 @@ __device__ __forceinline__ void copy_async_f32x4(float* to_shared, const float* 
 // CHUNK: tokens whose q, k, g, v and beta are staged in shared memory at a time; the next chunk is copied there
 // asynchronously (cp.async, zero fill for padding) while the present one is computed, so the recurrence never waits for
 // global memory inside a chunk.
-template <int LANES, int ROWS, int CHUNK>
+constexpr int RULE_DELTA = 0, RULE_DECAYED_SUM = 1, RULE_BONUS_READ = 2;
+
+template <int LANES, int ROWS, int CHUNK, int RULE>
 __global__ void __launch_bounds__(SCAN_COLS * LANES) delta_scan_kernel(ScanParams p) {
     pdl_prologue();
     constexpr int SCAN_LANES = LANES, SCAN_THREADS = SCAN_COLS * LANES;
@@ -163,12 +170,17 @@ __global__ void __launch_bounds__(SCAN_COLS * LANES) delta_scan_kernel(ScanParam
 #pragma unroll
     for (int i = 0; i < ROWS; ++i)
         S[i] = (!fresh && col_ok && row_of(i) < p.DK) ? st[(size_t)row_of(i) * p.DV + col] : 0.0f;
+    float U[RULE == RULE_BONUS_READ ? ROWS : 1];
+    if (RULE == RULE_BONUS_READ) {
+#pragma unroll
+        for (int i = 0; i < ROWS; ++i) U[i] = row_of(i) < p.DK ? p.bonus[(size_t)h * p.DK + row_of(i)] : 0.0f;
+    }
 
     const float* const q_base = p.qn + ((size_t)start * p.G + kvh) * p.DK;
     const float* const k_base = p.kn + ((size_t)start * p.G + kvh) * p.DK;
     const float* const g_base = p.g + ((size_t)start * p.H + h) * p.DK;
     const float* const v_base = p.v + (size_t)start * p.ld_v + (size_t)h * p.DV;
-    const float* const b_base = p.beta + (size_t)start * p.H + h;
+    const float* const b_base = p.beta ? p.beta + (size_t)start * p.H + h : g_base;     // without beta: any readable address, the value is unused
     const size_t qk_pitch = (size_t)p.G * p.DK, g_pitch = (size_t)p.H * p.DK;
     // the chunk that begins at token `first` into staging buffer `buf`; padding (rows beyond DK, columns beyond DV,
     // tokens beyond the sequence's) becomes zero: a zero k and q keep such rows of S at zero whatever g is
@@ -227,6 +239,34 @@ __global__ void __launch_bounds__(SCAN_COLS * LANES) delta_scan_kernel(ScanParam
             const float4* gs = reinterpret_cast<const float4*>(row + 2 * DKP) + part;
             const float v = row[3 * DKP + local_col], beta = row[3 * DKP + SCAN_COLS];
             float4 kk[ROWS / 4];
+            if (RULE != RULE_DELTA) {
+                // S <- diag(g) S + k v^T with the read-out S^T q behind it (decayed sum), or in front of it with the
+                // bonus u on the present token's own k v^T (bonus read); one meeting of the lanes a token
+                float o0 = 0.0f, o1 = 0.0f, o2 = 0.0f, o3 = 0.0f;
+#pragma unroll
+                for (int j = 0; j < ROWS / 4; ++j) {
+                    const float4 gg = gs[j * LANES], qq = qs[j * LANES];
+                    kk[j] = ks[j * LANES];
+                    const float kv0 = kk[j].x * v, kv1 = kk[j].y * v, kv2 = kk[j].z * v, kv3 = kk[j].w * v;
+                    if (RULE == RULE_BONUS_READ) {
+                        o0 = fmaf(fmaf(U[4 * j + 0], kv0, S[4 * j + 0]), qq.x, o0); o1 = fmaf(fmaf(U[4 * j + 1], kv1, S[4 * j + 1]), qq.y, o1);
+                        o2 = fmaf(fmaf(U[4 * j + 2], kv2, S[4 * j + 2]), qq.z, o2); o3 = fmaf(fmaf(U[4 * j + 3], kv3, S[4 * j + 3]), qq.w, o3);
+                    }
+                    S[4 * j + 0] = fmaf(S[4 * j + 0], gg.x, kv0); S[4 * j + 1] = fmaf(S[4 * j + 1], gg.y, kv1);
+                    S[4 * j + 2] = fmaf(S[4 * j + 2], gg.z, kv2); S[4 * j + 3] = fmaf(S[4 * j + 3], gg.w, kv3);
+                    if (RULE == RULE_DECAYED_SUM) {
+                        o0 = fmaf(S[4 * j + 0], qq.x, o0); o1 = fmaf(S[4 * j + 1], qq.y, o1);
+                        o2 = fmaf(S[4 * j + 2], qq.z, o2); o3 = fmaf(S[4 * j + 3], qq.w, o3);
+                    }
+                }
+                float out = (o0 + o1) + (o2 + o3);
+                out += __shfl_xor_sync(0xffffffffu, out, 1);
+                out += __shfl_xor_sync(0xffffffffu, out, 2);
+                out += __shfl_xor_sync(0xffffffffu, out, 4);
+                if (LANES == 16) out += __shfl_xor_sync(0xffffffffu, out, 8);
+                if (part == 0 && col_ok) o_at[(size_t)tok * ((size_t)p.H * p.DV)] = out;
+                return;
+            }
             float d0 = 0.0f, d1 = 0.0f, d2 = 0.0f, d3 = 0.0f;          // four chains instead of one (always the same four)
 #pragma unroll
             for (int j = 0; j < ROWS / 4; ++j) {
@@ -317,25 +357,26 @@ __global__ void __launch_bounds__(WARPS * 32) delta_output_kernel(OutputParams p
 }
 
 // out[t, c] = src[t, col0 + c] (partial results summed in split order), stored in the compute dtype: the narrow output of
-// a first projection made ready for the second one.
+// a first projection made ready for the second one (`activation` 1: its tanh).
 template <typename OutT>
-__global__ void take_columns_kernel(Columns src, int col0, int n, int T, OutT* out) {
+__global__ void take_columns_kernel(Columns src, int col0, int n, int T, OutT* out, int activation) {
     pdl_prologue();
     const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= (long long)T * n) return;
-    out[i] = from_f32<OutT>(src.at(i / n, col0 + (int)(i % n)));
+    const float v = src.at(i / n, col0 + (int)(i % n));
+    out[i] = from_f32<OutT>(activation == 1 ? tanhf(v) : v);
 }
 
 }  // namespace
 
 MLB_EXPORT int mlb_take_columns(const float* src, long long ld, int n_partials, long long partial_stride, int col0, int n, int T,
-                                void* out, int out_dtype, cudaStream_t stream) {
-    if (!src || !out || n <= 0 || T < 0) return fail(MLB_INVALID_ARGUMENT, "take_columns: bad operands");
+                                void* out, int out_dtype, int activation, cudaStream_t stream) {
+    if (!src || !out || n <= 0 || T < 0 || activation < 0 || activation > 1) return fail(MLB_INVALID_ARGUMENT, "take_columns: bad operands");
     if (T == 0) return MLB_OK;
     Columns c{src, ld, n_partials < 1 ? 1 : n_partials, partial_stride};
     const unsigned blocks = (unsigned)(((long long)T * n + 255) / 256);
-    if (out_dtype == MLB_BF16) launch_kernel(take_columns_kernel<__nv_bfloat16>, blocks, 256, 0, stream, c, col0, n, T, (__nv_bfloat16*)out);
-    else launch_kernel(take_columns_kernel<float>, blocks, 256, 0, stream, c, col0, n, T, (float*)out);
+    if (out_dtype == MLB_BF16) launch_kernel(take_columns_kernel<__nv_bfloat16>, blocks, 256, 0, stream, c, col0, n, T, (__nv_bfloat16*)out, activation);
+    else launch_kernel(take_columns_kernel<float>, blocks, 256, 0, stream, c, col0, n, T, (float*)out, activation);
     return check_launch("take_columns");
 }
 
@@ -355,17 +396,21 @@ MLB_EXPORT int mlb_delta_prepare(const float* qkv, long long ld_qkv, const float
     return check_launch("delta_prepare");
 }
 
-MLB_EXPORT int mlb_delta_scan(const float* qn, const float* kn, const float* g, const float* beta, const float* v, long long ld_v,
-                              float* o, float* state, const int* slots, int num_slots, const int* seq_starts, const int* seq_pos0,
-                              int A, int H, int G, int DK, int DV, int* error_flag, cudaStream_t stream) {
+namespace {
+
+template <int RULE>
+int launch_scan(const float* qn, const float* kn, const float* g, const float* beta, const float* bonus, const float* v, long long ld_v,
+                float* o, float* state, const int* slots, int num_slots, const int* seq_starts, const int* seq_pos0,
+                int A, int H, int G, int DK, int DV, int* error_flag, cudaStream_t stream) {
     if (A < 0 || H <= 0 || G <= 0 || H % G || DK <= 0 || DK > MAX_D || DV <= 0)
-        return fail(MLB_UNSUPPORTED_SIZE, "delta_scan: heads %d/%d, widths %d (at most %d) / %d", H, G, DK, MAX_D, DV);
-    if (!qn || !kn || !g || !beta || !v || !o || !state || !slots || !seq_starts || !seq_pos0)
-        return fail(MLB_INVALID_ARGUMENT, "delta_scan: null operand");
+        return fail(MLB_UNSUPPORTED_SIZE, "scan: heads %d/%d, widths %d (at most %d) / %d", H, G, DK, MAX_D, DV);
+    if (!qn || !kn || !g || (RULE == RULE_DELTA && !beta) || (RULE == RULE_BONUS_READ && !bonus) || !v || !o || !state || !slots ||
+        !seq_starts || !seq_pos0)
+        return fail(MLB_INVALID_ARGUMENT, "scan: null operand");
     if (A == 0) return MLB_OK;
     const bool aligned = ((uintptr_t)qn | (uintptr_t)kn | (uintptr_t)g | (uintptr_t)v) % 16 == 0;
     const int vec = aligned && DK % 4 == 0 && DV % 4 == 0 && ld_v % 4 == 0;
-    ScanParams p{qn, kn, g, beta, v, ld_v, o, state, slots, num_slots, seq_starts, seq_pos0, A, H, G, DK, DV, vec, error_flag};
+    ScanParams p{qn, kn, g, beta, bonus, v, ld_v, o, state, slots, num_slots, seq_starts, seq_pos0, A, H, G, DK, DV, vec, error_flag};
     const unsigned blocks = (unsigned)((long long)A * H * ((DV + SCAN_COLS - 1) / SCAN_COLS));
     // A handful of long-running CTAs (a prompt portion: one CTA walks all its tokens) must be spread one to an SM.  Started
     // early behind a predecessor that still fills the SMs, they land wherever a slot falls free, several on one SM, and
@@ -375,11 +420,34 @@ MLB_EXPORT int mlb_delta_scan(const float* qn, const float* kn, const float* g, 
         if (early) launch_kernel(kernel, blocks, SCAN_COLS * lanes, 0, stream, p);
         else kernel<<<blocks, SCAN_COLS * lanes, 0, stream>>>(p);
     };
-    if (DK <= 32) go(delta_scan_kernel<8, 4, 16>, 8);
-    else if (DK <= 64) go(delta_scan_kernel<16, 4, 16>, 16);
-    else if (DK <= 128) go(delta_scan_kernel<16, 8, 8>, 16);
-    else go(delta_scan_kernel<16, 16, 4>, 16);
-    return check_launch("delta_scan");
+    if (DK <= 32) go(delta_scan_kernel<8, 4, 16, RULE>, 8);
+    else if (DK <= 64) go(delta_scan_kernel<16, 4, 16, RULE>, 16);
+    else if (DK <= 128) go(delta_scan_kernel<16, 8, 8, RULE>, 16);
+    else go(delta_scan_kernel<16, 16, 4, RULE>, 16);
+    return check_launch("scan");
+}
+
+}  // namespace
+
+MLB_EXPORT int mlb_delta_scan(const float* qn, const float* kn, const float* g, const float* beta, const float* v, long long ld_v,
+                              float* o, float* state, const int* slots, int num_slots, const int* seq_starts, const int* seq_pos0,
+                              int A, int H, int G, int DK, int DV, int* error_flag, cudaStream_t stream) {
+    return launch_scan<RULE_DELTA>(qn, kn, g, beta, nullptr, v, ld_v, o, state, slots, num_slots, seq_starts, seq_pos0, A, H, G, DK, DV,
+                                   error_flag, stream);
+}
+
+// rule 1: S <- diag(g) S + k v^T, o = S^T q;   rule 2: o = (S + diag(bonus) k v^T)^T q, then S <- diag(g) S + k v^T.
+// q, k [T, G * DK], g [T, H * DK], bonus [H, DK] (rule 2), v rows of pitch ld_v, o [T, H * DV], state [slots, H, DK, DV].
+MLB_EXPORT int mlb_linear_scan(int rule, const float* q, const float* k, const float* g, const float* bonus, const float* v,
+                               long long ld_v, float* o, float* state, const int* slots, int num_slots, const int* seq_starts,
+                               const int* seq_pos0, int A, int H, int G, int DK, int DV, int* error_flag, cudaStream_t stream) {
+    if (rule == RULE_DECAYED_SUM)
+        return launch_scan<RULE_DECAYED_SUM>(q, k, g, nullptr, nullptr, v, ld_v, o, state, slots, num_slots, seq_starts, seq_pos0, A, H, G,
+                                             DK, DV, error_flag, stream);
+    if (rule == RULE_BONUS_READ)
+        return launch_scan<RULE_BONUS_READ>(q, k, g, nullptr, bonus, v, ld_v, o, state, slots, num_slots, seq_starts, seq_pos0, A, H, G,
+                                            DK, DV, error_flag, stream);
+    return fail(MLB_INVALID_ARGUMENT, "linear_scan: unknown rule %d", rule);
 }
 
 MLB_EXPORT int mlb_delta_output(const float* o, const float* weight, const float* proj, long long ld_proj, int n_partials,

@@ -1,0 +1,239 @@
+// What surrounds a linear recurrence with a decay per key channel (the scan itself is mlb_linear_scan in delta_rule.cu).
+// fp32 arithmetic throughout; only what a product reads next is stored in the compute dtype.
+//
+//   mlb_token_shift        y_s[t] = x[t] + (x[t-1] - x[t]) * mu_s   for s = 0..n_mix-1: every projection of a mixer reads its
+//                          own blend of a token's input and the previous token's.  x[t-1] of a step's first token is the
+//                          sequence's state row (zeros at position 0).
+//   mlb_token_shift_state  the state row becomes the input of the step's last token (a kernel of its own behind the first:
+//                          every blend of the step reads the old state).
+//   mlb_decay_prepare      q * q_scale, k, v gathered out of projections' fp32 outputs (K-split partial results are summed in
+//                          split order) and the decay of every (token, head, key channel) from z = W2 act(a) + bias, where a is
+//                          the narrow output of a first projection (W2 a may come ready-made from a product):
+//                          form 0: sigmoid(z)^(1/tau) = exp(log_sigmoid(z) / tau);  form 1: exp(-exp(z)).
+//   mlb_head_norm_gate     o / sqrt(mean(o^2) + eps) per head, times a weight (one row of DV shared by the heads, or H * DV),
+//                          times act(gate) with the gate read from a projection's fp32 output (sigmoid or silu).
+#include "common.cuh"
+
+using namespace mlb;
+
+MLB_DEFINE_LAST_ERROR()
+
+namespace {
+
+constexpr int WARPS = 4;
+constexpr int MAX_D = 256;
+constexpr int PER_LANE = MAX_D / 32;
+
+struct Columns {               // a block of columns of fp32 rows, possibly K-split partial results
+    const float* base; long long ld; int n_partials; long long partial_stride;
+    __device__ __forceinline__ float at(long long row, int col) const {
+        const float* p = base + row * ld + col;
+        float v = p[0];
+        for (int k = 1; k < n_partials; ++k) v += p[(size_t)k * partial_stride];
+        return v;
+    }
+};
+
+__device__ __forceinline__ float sigmoid(float v) {
+    if (v >= 0.0f) return 1.0f / (1.0f + expf(-v));
+    const float e = expf(v);
+    return e / (1.0f + e);
+}
+
+// log(sigmoid(v)) without overflow on either side
+__device__ __forceinline__ float log_sigmoid(float v) { return fminf(v, 0.0f) - log1pf(expf(-fabsf(v))); }
+
+// ------------------------------------------------------------------------------ token shift
+template <typename T>
+__global__ void token_shift_kernel(const T* __restrict__ x, const float* __restrict__ mu, const float* __restrict__ state,
+                                   const int* __restrict__ slots, int num_slots, const int* __restrict__ seq_starts,
+                                   const int* __restrict__ seq_pos0, const int* __restrict__ token_seq, T* __restrict__ out,
+                                   int tokens, int width, int n_mix, int* error_flag) {
+    pdl_prologue();
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (long long)tokens * width) return;
+    const int t = (int)(i / width), c = (int)(i % width);
+    const int a = token_seq[t];
+    const float now = to_f32(x[i]);
+    float before;
+    if (t > seq_starts[a]) {
+        before = to_f32(x[i - width]);
+    } else if (seq_pos0[a] == 0) {
+        before = 0.0f;
+    } else {
+        const int slot = slots[a];
+        if (slot < 0 || slot >= num_slots) {
+            if (error_flag) atomicExch(error_flag, 3);
+            return;
+        }
+        before = state[(size_t)slot * width + c];
+    }
+    const float back = before - now;
+    for (int s = 0; s < n_mix; ++s)
+        out[((size_t)s * tokens + t) * width + c] = from_f32<T>(fmaf(back, mu[(size_t)s * width + c], now));
+}
+
+template <typename T>
+__global__ void token_shift_state_kernel(const T* __restrict__ x, float* __restrict__ state, const int* __restrict__ slots,
+                                         int num_slots, const int* __restrict__ seq_starts, int seqs, int width) {
+    pdl_prologue();
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (long long)seqs * width) return;
+    const int a = (int)(i / width), c = (int)(i % width);
+    const int last = seq_starts[a + 1] - 1, slot = slots[a];
+    if (last < seq_starts[a] || slot < 0 || slot >= num_slots) return;
+    state[(size_t)slot * width + c] = to_f32(x[(size_t)last * width + c]);
+}
+
+// ------------------------------------------------------------------------------ what enters the recurrence
+struct PrepareParams {
+    Columns q, k, v; int q_col, k_col, v_col;      // q, k: H * DK columns each; v: H * DV
+    float q_scale;
+    Columns narrow; int a_col; int rank; int narrow_act;      // a [rank] (narrow_act 1: tanh of it); used when `pre` has no base
+    const float* w2;                               // [H * DK, rank] fp32
+    Columns pre;                                   // W2 act(a) ready-made [T, H * DK]
+    const float* bias;                             // [H * DK], may be null
+    int form; float inv_tau;
+    float* q_out; float* k_out; float* v_out; float* decay;   // [T, H * DK] x 2, [T, H * DV], [T, H * DK]
+    int T, HK, HV;
+};
+
+__global__ void decay_prepare_kernel(PrepareParams p) {
+    pdl_prologue();
+    const int per_token = 3 * p.HK + p.HV;
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (long long)p.T * per_token) return;
+    const long long t = i / per_token;
+    int c = (int)(i % per_token);
+    if (c < p.HK) { p.q_out[t * p.HK + c] = p.q.at(t, p.q_col + c) * p.q_scale; return; }
+    c -= p.HK;
+    if (c < p.HK) { p.k_out[t * p.HK + c] = p.k.at(t, p.k_col + c); return; }
+    c -= p.HK;
+    if (c < p.HV) { p.v_out[t * p.HV + c] = p.v.at(t, p.v_col + c); return; }
+    c -= p.HV;
+    float z = 0.0f;
+    if (p.pre.base) {
+        z = p.pre.at(t, c);
+    } else {
+        const float* w = p.w2 + (size_t)c * p.rank;
+        for (int r = 0; r < p.rank; ++r) {
+            float a = p.narrow.at(t, p.a_col + r);
+            if (p.narrow_act == 1) a = tanhf(a);
+            z = fmaf(w[r], a, z);
+        }
+    }
+    if (p.bias) z += p.bias[c];
+    p.decay[t * p.HK + c] = p.form == 0 ? expf(log_sigmoid(z) * p.inv_tau) : expf(-expf(z));
+}
+
+// ------------------------------------------------------------------------------ output norm and gate
+struct OutputParams {
+    const float* o;                          // [T, H * DV]
+    const float* weight; int weight_per_head;      // [DV] shared by the heads (0) or [H * DV] (1); null: no weight
+    Columns gate; int gate_col; int gate_act;      // gate.base null: no gate; 0 sigmoid, 1 silu
+    void* out;                               // [T, H * DV]
+    int T, H, DV; float eps;
+};
+
+template <typename OutT>
+__global__ void __launch_bounds__(WARPS * 32) head_norm_gate_kernel(OutputParams p) {
+    pdl_prologue();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const long long item = (long long)blockIdx.x * WARPS + warp;
+    if (item >= (long long)p.T * p.H) return;
+    const int t = (int)(item / p.H), h = (int)(item % p.H);
+    const float* src = p.o + ((size_t)t * p.H + h) * p.DV;
+    float x[PER_LANE];
+    float ss = 0.0f;
+#pragma unroll
+    for (int i = 0; i < PER_LANE; ++i) {
+        const int c = lane + 32 * i;
+        x[i] = c < p.DV ? src[c] : 0.0f;
+        ss = fmaf(x[i], x[i], ss);
+    }
+    const float inv = 1.0f / sqrtf(warp_sum(ss) / (float)p.DV + p.eps);
+    OutT* dst = (OutT*)p.out + ((size_t)t * p.H + h) * p.DV;
+#pragma unroll
+    for (int i = 0; i < PER_LANE; ++i) {
+        const int c = lane + 32 * i;
+        if (c >= p.DV) continue;
+        float y = x[i] * inv;
+        if (p.weight) y *= p.weight[p.weight_per_head ? h * p.DV + c : c];
+        if (p.gate.base) {
+            const float g = p.gate.at(t, p.gate_col + h * p.DV + c);
+            y *= p.gate_act == 1 ? g * sigmoid(g) : sigmoid(g);
+        }
+        dst[c] = from_f32<OutT>(y);
+    }
+}
+
+}  // namespace
+
+MLB_EXPORT int mlb_token_shift(const void* x, int dtype, const float* mu, const float* state, const int* slots, int num_slots,
+                               const int* seq_starts, const int* seq_pos0, const int* token_seq, void* out, int tokens, int width,
+                               int n_mix, int* error_flag, cudaStream_t stream) {
+    if (tokens < 0 || width <= 0 || n_mix <= 0 || !x || !mu || !state || !slots || !seq_starts || !seq_pos0 || !token_seq || !out)
+        return fail(MLB_INVALID_ARGUMENT, "token_shift: bad operands");
+    if (tokens == 0) return MLB_OK;
+    const unsigned blocks = (unsigned)(((long long)tokens * width + 255) / 256);
+    if (dtype == MLB_BF16)
+        launch_kernel(token_shift_kernel<__nv_bfloat16>, blocks, 256, 0, stream, (const __nv_bfloat16*)x, mu, state, slots, num_slots,
+                      seq_starts, seq_pos0, token_seq, (__nv_bfloat16*)out, tokens, width, n_mix, error_flag);
+    else if (dtype == MLB_F32)
+        launch_kernel(token_shift_kernel<float>, blocks, 256, 0, stream, (const float*)x, mu, state, slots, num_slots, seq_starts,
+                      seq_pos0, token_seq, (float*)out, tokens, width, n_mix, error_flag);
+    else return fail(MLB_INVALID_ARGUMENT, "token_shift: unsupported dtype %d", dtype);
+    return check_launch("token_shift");
+}
+
+MLB_EXPORT int mlb_token_shift_state(const void* x, int dtype, float* state, const int* slots, int num_slots, const int* seq_starts,
+                                     int seqs, int width, cudaStream_t stream) {
+    if (seqs < 0 || width <= 0 || !x || !state || !slots || !seq_starts) return fail(MLB_INVALID_ARGUMENT, "token_shift_state: bad operands");
+    if (seqs == 0) return MLB_OK;
+    const unsigned blocks = (unsigned)(((long long)seqs * width + 255) / 256);
+    if (dtype == MLB_BF16)
+        launch_kernel(token_shift_state_kernel<__nv_bfloat16>, blocks, 256, 0, stream, (const __nv_bfloat16*)x, state, slots, num_slots,
+                      seq_starts, seqs, width);
+    else if (dtype == MLB_F32)
+        launch_kernel(token_shift_state_kernel<float>, blocks, 256, 0, stream, (const float*)x, state, slots, num_slots, seq_starts,
+                      seqs, width);
+    else return fail(MLB_INVALID_ARGUMENT, "token_shift_state: unsupported dtype %d", dtype);
+    return check_launch("token_shift_state");
+}
+
+MLB_EXPORT int mlb_decay_prepare(const float* q, long long q_ld, int q_partials, long long q_stride, int q_col,
+                                 const float* k, long long k_ld, int k_partials, long long k_stride, int k_col,
+                                 const float* v, long long v_ld, int v_partials, long long v_stride, int v_col, float q_scale,
+                                 const float* narrow, long long n_ld, int n_partials, long long n_stride, int a_col, int rank,
+                                 int narrow_act, const float* w2, const float* pre, long long pre_ld, int pre_partials,
+                                 long long pre_stride, const float* bias, int form, float tau, float* q_out, float* k_out,
+                                 float* v_out, float* decay, int T, int HK, int HV, cudaStream_t stream) {
+    if (T < 0 || HK <= 0 || HV <= 0 || !q || !k || !v || !q_out || !k_out || !v_out || !decay || (!pre && (!narrow || !w2 || rank <= 0)))
+        return fail(MLB_INVALID_ARGUMENT, "decay_prepare: bad operands");
+    if ((form != 0 && form != 1) || (form == 0 && !(tau > 0.0f))) return fail(MLB_INVALID_ARGUMENT, "decay_prepare: form %d, tau %g", form, tau);
+    if (T == 0) return MLB_OK;
+    auto cols = [](const float* base, long long ld, int n, long long stride) { return Columns{base, ld, n < 1 ? 1 : n, stride}; };
+    PrepareParams p{cols(q, q_ld, q_partials, q_stride), cols(k, k_ld, k_partials, k_stride), cols(v, v_ld, v_partials, v_stride),
+                    q_col, k_col, v_col, q_scale, cols(narrow, n_ld, n_partials, n_stride), a_col, rank, narrow_act, w2,
+                    cols(pre, pre_ld, pre_partials, pre_stride), bias, form, form == 0 ? 1.0f / tau : 0.0f, q_out, k_out, v_out, decay,
+                    T, HK, HV};
+    const long long n = (long long)T * (3 * HK + HV);
+    launch_kernel(decay_prepare_kernel, (unsigned)((n + 255) / 256), 256, 0, stream, p);
+    return check_launch("decay_prepare");
+}
+
+MLB_EXPORT int mlb_head_norm_gate(const float* o, const float* weight, int weight_per_head, const float* gate, long long gate_ld,
+                                  int gate_partials, long long gate_stride, int gate_col, int gate_act, void* out, int out_dtype,
+                                  int T, int H, int DV, float eps, cudaStream_t stream) {
+    if (T < 0 || H <= 0 || DV <= 0 || DV > MAX_D) return fail(MLB_UNSUPPORTED_SIZE, "head_norm_gate: value width %d (at most %d)", DV, MAX_D);
+    if (!o || !out) return fail(MLB_INVALID_ARGUMENT, "head_norm_gate: null operand");
+    if (T == 0) return MLB_OK;
+    OutputParams p{o, weight, weight_per_head, Columns{gate, gate_ld, gate_partials < 1 ? 1 : gate_partials, gate_stride}, gate_col,
+                   gate_act, out, T, H, DV, eps};
+    const long long items = (long long)T * H;
+    const unsigned blocks = (unsigned)((items + WARPS - 1) / WARPS);
+    if (out_dtype == MLB_BF16) launch_kernel(head_norm_gate_kernel<__nv_bfloat16>, blocks, WARPS * 32, 0, stream, p);
+    else if (out_dtype == MLB_F32) launch_kernel(head_norm_gate_kernel<float>, blocks, WARPS * 32, 0, stream, p);
+    else return fail(MLB_INVALID_ARGUMENT, "head_norm_gate: unsupported dtype %d", out_dtype);
+    return check_launch("head_norm_gate");
+}

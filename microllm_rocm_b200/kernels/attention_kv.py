@@ -20,11 +20,11 @@ MAX_WIDTH = 256
 
 ops.register_signatures("attention_kv.cu", {
     "mlb_qk_prepare": [c_void_p, c_longlong, c_int, c_longlong, c_int, c_int, c_int, c_void_p, c_longlong, c_int, c_longlong,
-                       c_void_p, c_void_p, c_float, c_void_p, c_int, c_float, c_float, c_int, c_void_p, c_void_p, c_void_p,
+                       c_void_p, c_void_p, c_float, c_int, c_void_p, c_int, c_float, c_float, c_int, c_void_p, c_void_p, c_void_p,
                        c_int, c_int, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
     "mlb_gate_heads": [c_void_p, c_void_p, c_int, c_void_p, c_longlong, c_int, c_longlong, c_int, c_int, c_int, c_int, c_int, c_void_p],
     "mlb_paged_attention_kv": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
-                               c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_longlong, c_int, c_longlong, c_int,
+                               c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_longlong, c_int, c_longlong, c_int,
                                c_void_p, c_void_p],
 })
 
@@ -56,8 +56,11 @@ def qk_prepare(src: torch.Tensor, q_col: int, k_col: int, v_col: int, *, kv_src:
                q_norm: Optional[torch.Tensor], k_norm: Optional[torch.Tensor], eps: float, freq: Optional[torch.Tensor],
                rot_dims: int, magnitude: float, q_temp, positions: torch.Tensor, token_seq: torch.Tensor,
                block_table: Optional[torch.Tensor], pages: Optional[torch.Tensor], page_size: int, q_out: torch.Tensor,
-               heads: int, kv_heads: int, dk: int, dv: int, error_flag: Optional[torch.Tensor], stored: Optional[int] = None) -> None:
-    """q, k, v are column blocks (first columns q_col, k_col, v_col) of `src`; k and v of `kv_src` when that is given.
+               heads: int, kv_heads: int, dk: int, dv: int, error_flag: Optional[torch.Tensor], stored: Optional[int] = None,
+               norm: Optional[str] = None) -> None:
+    """`norm`: None (rms norm of q and k in front of the rotation when their weights are given, else none), "before" or
+    "after" the rotation (a missing weight then means the plain quotient x / rms(x)).
+    q, k, v are column blocks (first columns q_col, k_col, v_col) of `src`; k and v of `kv_src` when that is given.
     `q_temp`: None or (coef, every).  `pages` None: only the queries are made.  `stored`: the width every query, key and
     value row is stored with (zeros behind its own elements), for an attention kernel that wants one width for all."""
     _, ld, n, stride = _columns(src, "src")
@@ -77,10 +80,13 @@ def qk_prepare(src: torch.Tensor, q_col: int, k_col: int, v_col: int, *, kv_src:
             raise KernelError(f"qk_prepare: pages {tuple(pages.shape)} do not match the head geometry")
         num_pages, max_blocks = pages.shape[0], block_table.shape[1]
     coef, every = (float(q_temp[0]), int(q_temp[1])) if q_temp else (0.0, 0)
+    if norm not in (None, "before", "after"):
+        raise KernelError(f"qk_prepare: norm {norm!r} is not 'before' or 'after'")
+    norm_where = {"before": 1, "after": 2}[norm] if norm else (1 if q_norm is not None and k_norm is not None else 0)
     L = ops.lib("attention_kv.cu")
     build.check(L, L.mlb_qk_prepare(
         src.data_ptr(), ld, n, stride, q_col, k_col, v_col, kv_ptr, kv_ld, kv_n, kv_stride, ops._ptr(q_norm), ops._ptr(k_norm),
-        float(eps), ops._ptr(freq) if rot_dims else None, int(rot_dims), float(magnitude), coef, every, positions.data_ptr(),
+        float(eps), norm_where, ops._ptr(freq) if rot_dims else None, int(rot_dims), float(magnitude), coef, every, positions.data_ptr(),
         token_seq.data_ptr(), ops._ptr(block_table), max_blocks, num_pages, page_size, q_out.data_ptr(), ops.dtype_tag(q_out),
         ops._ptr(pages), ops.dtype_tag(pages) if pages is not None else ops.F32, T, heads, kv_heads, dk, dv, sk, sv,
         ops._ptr(error_flag), ops._stream()))
@@ -105,8 +111,9 @@ def gate_heads(o: torch.Tensor, out: torch.Tensor, gate: Optional[torch.Tensor],
 def paged_attention_kv(q: torch.Tensor, pages: torch.Tensor, out: torch.Tensor, positions: torch.Tensor, token_seq: torch.Tensor,
                        block_table: torch.Tensor, page_size: int, heads: int, kv_heads: int, dk: int, dv: int, scale: float,
                        window: Optional[int], gate: Optional[torch.Tensor], gate_col: int,
-                       error_flag: Optional[torch.Tensor]) -> None:
-    """out[T, heads * dv] = softmax(q k^T * scale) v (* sigmoid(gate columns gate_col.. of fp32 rows or partial results))."""
+                       error_flag: Optional[torch.Tensor], chunk: Optional[int] = None) -> None:
+    """`chunk`: a query sees only the keys of its own block of `chunk` positions (blocks counted from position 0).
+    out[T, heads * dv] = softmax(q k^T * scale) v (* sigmoid(gate columns gate_col.. of fp32 rows or partial results))."""
     ops._need(q, "q", dims=2); ops._need(out, "out", dims=2); ops._need(block_table, "block_table", torch.int32, 2)
     T = q.shape[0]
     if q.shape[1] != heads * dk or out.shape != (T, heads * dv):
@@ -121,5 +128,5 @@ def paged_attention_kv(q: torch.Tensor, pages: torch.Tensor, out: torch.Tensor, 
     build.check(L, L.mlb_paged_attention_kv(
         q.data_ptr(), ops.dtype_tag(q), pages.data_ptr(), ops.dtype_tag(pages), out.data_ptr(), ops.dtype_tag(out),
         positions.data_ptr(), token_seq.data_ptr(), block_table.data_ptr(), block_table.shape[1], pages.shape[0], page_size, T,
-        heads, kv_heads, dk, dv, int(window or 0), float(scale), g_ptr, g_ld, g_n, g_stride, int(gate_col),
+        heads, kv_heads, dk, dv, int(window or 0), int(chunk or 0), float(scale), g_ptr, g_ld, g_n, g_stride, int(gate_col),
         ops._ptr(error_flag), ops._stream()))

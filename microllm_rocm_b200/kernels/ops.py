@@ -81,7 +81,7 @@ _SIGNATURES = {
     },
     "attention_plain.cu": {
         "mlb_paged_attention_plain": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p,
-                                      c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                                      c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                                       c_float, c_void_p, c_void_p],
     },
     "residual.cu": {
@@ -96,6 +96,10 @@ _SIGNATURES = {
         "mlb_layernorm": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_float, c_void_p],
         "mlb_scale_add_layernorm": [c_void_p, c_float, c_void_p, c_int, c_longlong, c_float, c_void_p, c_int, c_longlong, c_float,
                                     c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_void_p],
+    },
+    "post_norm.cu": {
+        "mlb_normed_add_rmsnorm": [c_void_p, c_void_p, c_int, c_longlong, c_float, c_void_p, c_int, c_longlong, c_float, c_void_p,
+                                   c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_void_p],
     },
     "sampling.cu": {
         "mlb_argmax_rows": [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p],
@@ -158,7 +162,8 @@ def part_sources():
     """(source, defines) of the kernels that only some kinds of parts ask for (each part names its own in
     `kernel_sources`)."""
     return [("residual.cu", {}), ("grouped_gemm.cu", {}), ("grouped_mma.cu", {}), ("latent.cu", {}), ("moe.cu", {}),
-            ("layernorm.cu", {}), ("short_conv.cu", {}), ("attention_kv.cu", {}), ("delta_rule.cu", {})]
+            ("layernorm.cu", {}), ("short_conv.cu", {}), ("attention_kv.cu", {}), ("delta_rule.cu", {}),
+            ("linear_attention.cu", {}), ("post_norm.cu", {})]
 
 
 def all_sources():
@@ -380,6 +385,32 @@ def scale_add_layernorm(x: torch.Tensor, alpha: float, terms, weight: torch.Tens
     build.check(L, L.mlb_scale_add_layernorm(x.data_ptr(), float(alpha), *args, weight.data_ptr(), bias.data_ptr(), _ptr(out),
                                              dtype_tag(out) if out is not None else F32, x.shape[0], x.shape[1], float(eps),
                                              _stream()))
+
+
+def normed_add_rmsnorm(x: torch.Tensor, terms, post_weight: torch.Tensor, eps: float, next_weight: Optional[torch.Tensor] = None,
+                       out: Optional[torch.Tensor] = None) -> None:
+    """d = sum_i s_i * d_i;  x += d / rms(d) * post_weight in place (fp32);  then, when `out` is given, out = x / rms(x) *
+    next_weight in out's dtype.  `terms`: one or two (s_i, d_i); a d_i may be [S, M, N] partial results, summed over S in order."""
+    _need(x, "x", torch.float32, 2); _need(post_weight, "post_weight", torch.float32, 1)
+    terms = list(terms)
+    if not 1 <= len(terms) <= 2:
+        raise KernelError("normed_add_rmsnorm: one or two terms")
+    if post_weight.shape[0] != x.shape[1]:
+        raise KernelError("normed_add_rmsnorm: shapes do not agree")
+    if out is not None:
+        _need(out, "out", dims=2); _need(next_weight, "next_weight", torch.float32, 1)
+        if out.shape != x.shape or next_weight.shape[0] != x.shape[1]:
+            raise KernelError("normed_add_rmsnorm: the normed copy must have the stream's shape")
+    args = []
+    for s, d in terms:
+        n, stride = _partials(d, x.shape, "normed_add_rmsnorm term")
+        args += [d.data_ptr(), n, stride, float(s)]
+    if len(terms) == 1:
+        args += [None, 0, 0, 0.0]
+    L = lib("post_norm.cu")
+    build.check(L, L.mlb_normed_add_rmsnorm(x.data_ptr(), *args, post_weight.data_ptr(), _ptr(next_weight) if out is not None else None,
+                                            _ptr(out), dtype_tag(out) if out is not None else F32, x.shape[0], x.shape[1], float(eps),
+                                            _stream()))
 
 
 # ------------------------------------------------------------------------------ scaled residual stream
@@ -616,7 +647,9 @@ def rope_table(positions: torch.Tensor, inv_freq: torch.Tensor, out: Optional[to
 def paged_attention_plain(q: torch.Tensor, pages: torch.Tensor, out: torch.Tensor, positions: torch.Tensor,
                           token_seq: torch.Tensor, block_table: torch.Tensor, num_heads: int, num_kv_heads: int,
                           head_dim: int, scale: float, window: Optional[int],
-                          error_flag: Optional[torch.Tensor]) -> None:
+                          error_flag: Optional[torch.Tensor], chunk: Optional[int] = None) -> None:
+    """`window`: only the last `window` keys (the query's own included); `chunk`: only keys of the query's own block of
+    `chunk` positions, blocks counted from position 0 of the sequence.  Both may be None."""
     _need(q, "q", dims=2); _need(pages, "pages", dims=5); _need(out, "out", dims=2)
     _need(positions, "positions", torch.int32, 1); _need(token_seq, "token_seq", torch.int32, 1)
     _need(block_table, "block_table", torch.int32, 2)
@@ -630,7 +663,7 @@ def paged_attention_plain(q: torch.Tensor, pages: torch.Tensor, out: torch.Tenso
     build.check(L, L.mlb_paged_attention_plain(
         q.data_ptr(), dtype_tag(q), pages.data_ptr(), dtype_tag(pages), out.data_ptr(), dtype_tag(out),
         positions.data_ptr(), token_seq.data_ptr(), block_table.data_ptr(), block_table.shape[1], num_pages,
-        page_size, T, num_heads, num_kv_heads, head_dim, int(window or 0), float(scale), _ptr(error_flag),
+        page_size, T, num_heads, num_kv_heads, head_dim, int(window or 0), int(chunk or 0), float(scale), _ptr(error_flag),
         _stream()))
 
 

@@ -25,7 +25,9 @@ ops.register_signatures("delta_rule.cu", {
     "mlb_delta_prepare": [c_void_p, c_longlong, c_void_p, c_longlong, c_int, c_longlong, c_int, c_int, c_void_p, c_void_p, c_longlong,
                           c_int, c_longlong, c_void_p, c_void_p,
                           c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p],
-    "mlb_take_columns": [c_void_p, c_longlong, c_int, c_longlong, c_int, c_int, c_int, c_void_p, c_int, c_void_p],
+    "mlb_take_columns": [c_void_p, c_longlong, c_int, c_longlong, c_int, c_int, c_int, c_void_p, c_int, c_int, c_void_p],
+    "mlb_linear_scan": [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_int,
+                        c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
     "mlb_delta_scan": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
                        c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
     "mlb_delta_output": [c_void_p, c_void_p, c_void_p, c_longlong, c_int, c_longlong, c_int, c_void_p, c_void_p, c_longlong, c_int,
@@ -76,15 +78,18 @@ def _pre(pre: Optional[torch.Tensor], T: int, width: int, what: str):
     return pre.data_ptr(), ld, n, stride
 
 
-def take_columns(src: torch.Tensor, col0: int, out: torch.Tensor) -> None:
-    """out[t, c] = src[t, col0 + c], `src` fp32 rows or their [S, T, N] partial results (summed), in out's dtype."""
+def take_columns(src: torch.Tensor, col0: int, out: torch.Tensor, activation: Optional[str] = None) -> None:
+    """out[t, c] = act(src[t, col0 + c]), `src` fp32 rows or their [S, T, N] partial results (summed), in out's dtype;
+    `activation` None or "tanh"."""
+    if activation not in (None, "tanh"):
+        raise KernelError(f"take_columns: activation {activation!r}")
     _, ld, n, stride = _columns(src, "src")
     ops._need(out, "out", dims=2)
     if out.shape[0] != src.shape[-2] or col0 < 0 or col0 + out.shape[1] > ld:
         raise KernelError("take_columns: shapes do not agree")
     L = ops.lib("delta_rule.cu")
     build.check(L, L.mlb_take_columns(src.data_ptr(), ld, n, stride, col0, out.shape[1], out.shape[0], out.data_ptr(),
-                                      ops.dtype_tag(out), ops._stream()))
+                                      ops.dtype_tag(out), 1 if activation == "tanh" else 0, ops._stream()))
 
 
 def delta_prepare(qkv: torch.Tensor, proj: torch.Tensor, beta_col: int, a_col: int, w2: Optional[torch.Tensor], dt_bias: torch.Tensor,
@@ -144,3 +149,34 @@ def delta_output(o: torch.Tensor, weight: torch.Tensor, proj: torch.Tensor, g_co
     L = ops.lib("delta_rule.cu")
     build.check(L, L.mlb_delta_output(o.data_ptr(), weight.data_ptr(), proj.data_ptr(), ld, n, stride, g_col, ops._ptr(w2), *pre_args,
                                       out.data_ptr(), ops.dtype_tag(out), T, heads, dv, rank, float(eps), ops._stream()))
+
+
+RULES = {"decayed_sum": 1, "bonus_read": 2}
+
+
+def linear_scan(rule: str, q: torch.Tensor, k: torch.Tensor, decay: torch.Tensor, v: torch.Tensor, o: torch.Tensor, state: torch.Tensor,
+                slots: torch.Tensor, ctx, heads: int, dk: int, dv: int, bonus: Optional[torch.Tensor] = None) -> None:
+    """A recurrence with one decay per head and key channel over the step's tokens, per head with S [dk, dv]:
+      "decayed_sum":  S <- diag(decay_t) S + k_t v_t^T;  o_t = S^T q_t
+      "bonus_read":   o_t = (S + diag(bonus) k_t v_t^T)^T q_t;  then S <- diag(decay_t) S + k_t v_t^T
+    q, k, decay [T, heads * dk] and v, o [T, heads * dv] fp32; `state` [slots, heads, dk, dv] fp32 (taken as zero for a
+    sequence that starts at position 0); `bonus` [heads, dk]."""
+    if rule not in RULES:
+        raise KernelError(f"linear_scan: rule {rule!r} is not one of {', '.join(RULES)}")
+    T = q.shape[0]
+    for name, t, shape in (("q", q, (T, heads * dk)), ("k", k, (T, heads * dk)), ("decay", decay, (T, heads * dk)),
+                           ("v", v, (T, heads * dv)), ("o", o, (T, heads * dv))):
+        ops._need(t, name, torch.float32, 2)
+        if tuple(t.shape) != shape:
+            raise KernelError(f"linear_scan: {name} must be {shape}, got {tuple(t.shape)}")
+    ops._need(state, "state", torch.float32, 4)
+    if tuple(state.shape[1:]) != (heads, dk, dv):
+        raise KernelError(f"linear_scan: the state must be [slots, {heads}, {dk}, {dv}], got {tuple(state.shape)}")
+    if rule == "bonus_read":
+        ops._need(bonus, "bonus", torch.float32, 2)
+        if tuple(bonus.shape) != (heads, dk):
+            raise KernelError(f"linear_scan: bonus must be [{heads}, {dk}]")
+    L = ops.lib("delta_rule.cu")
+    build.check(L, L.mlb_linear_scan(RULES[rule], q.data_ptr(), k.data_ptr(), decay.data_ptr(), ops._ptr(bonus), v.data_ptr(), v.stride(0),
+                                     o.data_ptr(), state.data_ptr(), slots.data_ptr(), state.shape[0], ctx.seq_starts.data_ptr(),
+                                     ctx.seq_pos0.data_ptr(), ctx.num_seqs, heads, heads, dk, dv, ops._ptr(ctx.error_flag), ops._stream()))

@@ -2,5 +2,5 @@ from .base import (Runtime, WeightSpec, PagedKVNeed, PagedRowsNeed, FixedStateNe
                    PositionEncoding, RotaryTable, Mixer, FeedForward, Block, NORMS, POSITION_ENCODINGS, MIXERS,
                    FEED_FORWARDS, BLOCKS, EMBEDDINGS, HEADS, register_norm, register_position_encoding,
                    register_mixer, register_feed_forward, register_block, register_embedding, register_head)
-from . import norm, rotary, positions, attention, latent_attention, mlp, routed, embedding, block, loop, delta_rule, parallel  # noqa: F401  (register the built-in kinds)
+from . import norm, rotary, positions, attention, latent_attention, mlp, routed, embedding, block, loop, delta_rule, linear_attention, parallel  # noqa: F401  (register the built-in kinds)
 from .build import Model, build_model

@@ -159,11 +159,13 @@ class NormedAttention(Mixer):
       q, k, v = Wq x, Wk x, Wv x          `values="keys"`: there is no Wv and v is k AS PROJECTED (before norm and rotation)
       short causal convolution over time on every channel of q, k, v (`conv` taps > 1; weights [channels, taps], the last
           column is the current token's; the last taps - 1 projected rows of a sequence are kept in its state slot)
-      per-head rms norm of q and k with one weight each, shared by the heads (`qk_norm`)
+      per-head rms norm of q and k with one weight each, shared by the heads (`qk_norm`; `qk_norm_weight=False`: the
+          plain quotient x / rms(x), no tensors; `qk_norm_where="after"`: behind the rotation instead of in front of it)
       rotation of the first `rotary_dim` elements of every head by the position encoding's table, in interleaved
           pairs (2i, 2i + 1), cosines and sines times the table's magnitude (a split-half table is refused)
       q times 1 + coef * ln(floor((p + 1) / every) + 1) at position p (`q_temp = (coef, every)`)
-      score = q . k * scale, causal (optionally the last `window` keys), softmax
+      score = q . k * scale, causal (optionally the last `window` keys; optionally only the keys of the query's own
+          block of `chunk` positions, blocks counted from position 0 of the sequence), softmax
       concat_heads(o) * sigmoid(Wg x) (`gate`), then Wo
 
     Keys have `dim` elements per head and values `vdim`; the cache holds both widths (`PagedKVNeed.value_dim`).  All
@@ -185,6 +187,13 @@ class NormedAttention(Mixer):
         self.qk_norm = bool(params.get("qk_norm", True))
         self.q_temp = tuple(params["q_temp"]) if params.get("q_temp") else None
         self.window = params.get("window")
+        self.chunk = int(params["chunk"]) if params.get("chunk") else None
+        self.norm_weight = bool(params.get("qk_norm_weight", True))
+        self.norm_where = params.get("qk_norm_where", "before")
+        if self.norm_where not in ("before", "after"):
+            raise ValueError(f"normed_attention: qk_norm_where {self.norm_where!r} is not 'before' or 'after'")
+        if self.chunk is not None and self.chunk <= 0:
+            raise ValueError("normed_attention: chunk must be positive")
         if self.values not in ("projected", "keys"):
             raise ValueError(f"normed_attention: values {self.values!r} is not 'projected' or 'keys'")
         if self.values == "keys" and self.dv != self.dk:
@@ -242,7 +251,7 @@ class NormedAttention(Mixer):
             specs[n["v"]] = WeightSpec((self.v_cols, self.hidden))
         if self.has_gate:
             specs[n["gate"]] = WeightSpec((self.g_cols, self.hidden))
-        if self.qk_norm:
+        if self.qk_norm and self.norm_weight:
             specs[n["q_norm"]] = WeightSpec((self.dk,), role="vector", init=("one_plus_normal", 0.1))
             specs[n["k_norm"]] = WeightSpec((self.dk,), role="vector", init=("one_plus_normal", 0.1))
         if self.taps > 1:
@@ -282,15 +291,15 @@ class NormedAttention(Mixer):
                 keys = ["q_conv", "k_conv"] + (["v_conv"] if self.v_cols else [])
                 self.w_conv = torch.cat([tensors[n[k]] for k in keys], 0).contiguous()
         self.w_o = tensors[n["o"]]
-        self.q_norm_w = tensors[n["q_norm"]] if self.qk_norm else None
-        self.k_norm_w = tensors[n["k_norm"]] if self.qk_norm else None
+        self.q_norm_w = tensors[n["q_norm"]] if self.qk_norm and self.norm_weight else None
+        self.k_norm_w = tensors[n["k_norm"]] if self.qk_norm and self.norm_weight else None
 
     def replay_key(self):
         if not self.rt.is_fp32 and not gemm_bf16._direct_library(self.rt.device):
             return None
         rotary = None if self.freq is None else (self.freq.data_ptr(), self.rot_dims, self.magnitude)
         return ("normed_attention", self.hidden, self.nh, self.nkv, self.dk, self.dv, self.scale, self.eps, self.values, self.taps,
-                self.has_gate, self.qk_norm, self.q_temp, self.window, rotary)
+                self.has_gate, self.qk_norm, self.norm_weight, self.norm_where, self.q_temp, self.window, self.chunk, rotary)
 
     def own_tensors(self):
         return [self.w_in, self.w_o, self.q_norm_w, self.k_norm_w, self.w_conv]
@@ -329,21 +338,24 @@ class NormedAttention(Mixer):
                                 rot_dims=self.rot_dims, magnitude=self.magnitude, q_temp=self.q_temp, positions=ctx.positions,
                                 token_seq=ctx.token_seq, block_table=kv_view.block_table,
                                 pages=kv_view.pages if kv_view.writable else None, page_size=kv_view.page_size, q_out=q,
-                                heads=self.nh, kv_heads=self.nkv, dk=self.dk, dv=self.dv, error_flag=flag, stored=self.stored)
+                                heads=self.nh, kv_heads=self.nkv, dk=self.dk, dv=self.dv, error_flag=flag, stored=self.stored,
+                                norm=self.norm_where if self.qk_norm else None)
         o = ctx.buffer("normed_attention.o", (T, self.nh * self.dv), dt)
         gate = proj if self.has_gate else None
         if self._shared_kernels(kv_view.page_size):
             wide = o if (sv == self.dv and gate is None) else ctx.buffer("normed_attention.o_stored", (T, self.nh * sv), dt)
             attention_kernels.paged_attention(q, kv_view.pages, wide, ctx, kv_view.block_table, self.nh, self.nkv, sk, self.scale,
-                                              self.window, beside_mma_products=gemm_bf16.gemv_preferred(x, self.w_o))
+                                              self.window, beside_mma_products=gemm_bf16.gemv_preferred(x, self.w_o), chunk=self.chunk)
             if wide is not o:
                 attention_kv.gate_heads(wide, o, gate, self.conv_cols, self.nh, self.dv, sv)
         elif self.stored is not None:            # a page size the tensor-core kernels do not take: the plain kernel of one width
             wide = ctx.buffer("normed_attention.o_stored", (T, self.nh * sv), dt)
-            attention_kernels.paged_attention(q, kv_view.pages, wide, ctx, kv_view.block_table, self.nh, self.nkv, sk, self.scale, self.window)
+            attention_kernels.paged_attention(q, kv_view.pages, wide, ctx, kv_view.block_table, self.nh, self.nkv, sk, self.scale, self.window,
+                                              chunk=self.chunk)
             attention_kv.gate_heads(wide, o, gate, self.conv_cols, self.nh, self.dv, sv)
         else:
             attention_kv.paged_attention_kv(q, kv_view.pages, o, ctx.positions, ctx.token_seq, kv_view.block_table, kv_view.page_size,
-                                            self.nh, self.nkv, self.dk, self.dv, self.scale, self.window, gate, self.conv_cols, flag)
+                                            self.nh, self.nkv, self.dk, self.dv, self.scale, self.window, gate, self.conv_cols, flag,
+                                            chunk=self.chunk)
         return linear(o, self.w_o, None, torch.float32, partials_ok=True, error_flag=flag,
                       alloc=lambda shape, dtype: ctx.buffer("normed_attention.out", shape, dtype))

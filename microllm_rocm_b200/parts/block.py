@@ -150,3 +150,58 @@ class PostNormResidualBlock(Block):
         if copy is not None:
             ctx.step_values["block.stream_copy_of"] = residual.data_ptr()
         return residual, None
+
+
+@register_block("sandwich_residual")
+class SandwichResidualBlock(Block):
+    """A norm on both sides of every sublayer:  x += post1(mixer(pre1(x)));  x += post2(feed_forward(pre2(x))), all four rms
+    norms with weights.  The two norms in front are the layer's `mixer_norm` and `ffn_norm`; the two behind are the block's
+    own tensors (`post_names`).  A sublayer's result is normalised, added, and the stream normalised again for the next
+    sublayer in ONE kernel; a mixer that is several mixers side by side hands over its weighted terms (`forward_terms`) and
+    that kernel adds them.  The stream that leaves the block is final (no delta is handed on)."""
+    carries_no_delta = True
+
+    def __init__(self, params: dict, rt: Runtime, mixer_norm: Norm, mixer: Mixer, ffn_norm: Norm, feed_forward: FeedForward):
+        self.rt = rt
+        self.prefix = params.get("prefix", "")
+        self.size, self.eps = int(params["size"]), float(params["eps"])
+        self.post_names = tuple(params.get("post_names", ("post_mixer_norm.weight", "post_ffn_norm.weight")))
+        self.mixer_norm, self.mixer, self.ffn_norm, self.feed_forward = mixer_norm, mixer, ffn_norm, feed_forward
+        self.has_ff = not getattr(feed_forward, "absent", False)
+        if self.has_ff and not (hasattr(ffn_norm, "weight") and getattr(ffn_norm, "eps", None) == self.eps and hasattr(ffn_norm, "size")):
+            raise TypeError("sandwich_residual fuses the norm in front of the feed-forward: it must be an rms norm with the block's eps")
+        self.w_post1: Optional[torch.Tensor] = None
+        self.w_post2: Optional[torch.Tensor] = None
+
+    def weight_specs(self) -> Dict[str, WeightSpec]:
+        names = self.post_names if self.has_ff else self.post_names[:1]
+        return {n: WeightSpec((self.size,), role="vector", init=("one_plus_normal", 0.1)) for n in names}
+
+    def kernel_sources(self):
+        return [("post_norm.cu", {})]
+
+    def bind(self, tensors):
+        self.w_post1 = tensors[self.post_names[0]]
+        self.w_post2 = tensors[self.post_names[1]] if self.has_ff else None
+
+    def replay_key(self):
+        keys = [p.replay_key() for p in (self.mixer_norm, self.mixer, self.ffn_norm, self.feed_forward)]
+        return None if any(k is None for k in keys) else ("sandwich_residual", self.rt.dtype, self.size, self.eps, *keys)
+
+    def own_tensors(self):
+        own = [t for p in (self.mixer_norm, self.mixer, self.ffn_norm, self.feed_forward) for t in p.own_tensors()]
+        return own + [self.w_post1, self.w_post2]
+
+    def forward(self, residual: torch.Tensor, delta: Optional[torch.Tensor], ctx: StepContext, cache):
+        if delta is not None:            # a block of another arrangement ran before this one
+            ops.add_inplace(residual, delta)
+        normed = ctx.buffer("block.normed", tuple(residual.shape), self.rt.dtype)
+        self.mixer_norm.forward(residual, normed)
+        terms = self.mixer.forward_terms(normed, ctx, cache) if hasattr(self.mixer, "forward_terms") else [(1.0, self.mixer.forward(normed, ctx, cache))]
+        if not self.has_ff:
+            ops.normed_add_rmsnorm(residual, terms, self.w_post1, self.eps)
+            return residual, None
+        normed2 = ctx.buffer("block.normed2", tuple(residual.shape), self.rt.dtype)
+        ops.normed_add_rmsnorm(residual, terms, self.w_post1, self.eps, next_weight=self.ffn_norm.weight, out=normed2)
+        ops.normed_add_rmsnorm(residual, [(1.0, self.feed_forward.forward(normed2, ctx))], self.w_post2, self.eps)
+        return residual, None

@@ -20,17 +20,25 @@ class TokenEmbedding(Part):
         self.vocab = int(params["vocab_size"])
         self.hidden = int(params["hidden_size"])
         self.scale = float(params.get("scale", 1.0))       # the gathered rows are multiplied by it (fp32)
+        # an rms norm of the gathered rows with a weight of its own: (local name of the weight, eps), or None
+        self.norm = (str(params["norm"][0]), float(params["norm"][1])) if params.get("norm") else None
+        self.norm_weight: Optional[torch.Tensor] = None
         self.rt = rt
         self.table: Optional[torch.Tensor] = None
 
     def weight_specs(self) -> Dict[str, WeightSpec]:
-        return {self.name: WeightSpec((self.vocab, self.hidden), role="table")}
+        specs = {self.name: WeightSpec((self.vocab, self.hidden), role="table")}
+        if self.norm:
+            specs[self.norm[0]] = WeightSpec((self.hidden,), role="vector", init=("one_plus_normal", 0.1))
+        return specs
 
     def kernel_sources(self):
         return [("residual.cu", {})] if self.scale != 1.0 else []
 
     def bind(self, tensors):
         self.table = tensors[self.name]
+        if self.norm:
+            self.norm_weight = tensors[self.norm[0]]
 
     def forward(self, token_ids: torch.Tensor) -> torch.Tensor:
         out = torch.empty((token_ids.shape[0], self.hidden), dtype=torch.float32, device=token_ids.device)
@@ -38,6 +46,8 @@ class TokenEmbedding(Part):
             ops.embed_gather_scaled(self.table, token_ids, out, self.scale)
         else:
             ops.embed_gather(self.table, token_ids, out)
+        if self.norm:
+            ops.rmsnorm(out, self.norm_weight, self.norm[1], out)          # in place, fp32
         return out
 
 

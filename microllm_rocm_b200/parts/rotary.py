@@ -13,6 +13,10 @@ positions: with where(t) = rotary_dim * ln(original / (2 pi t)) / (2 ln theta) (
 over `original` positions), lo = max(floor(where(fast)), 0), hi = min(ceil(where(slow)), rotary_dim - 1) and
 ramp_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1), pair i turns with f_i / factor * ramp_i + f_i * (1 - ramp_i), and
 every cosine and sine is multiplied by 0.1 * ln(factor) + 1 (`RotaryTable.magnitude`).
+
+Optional `rescale` {factor, low, high, original} slows the long waves down: with wavelength l_i = 2 pi / f_i, pair i keeps
+f_i where l_i < original / high, turns with f_i / factor where l_i > original / low, and in between with
+(1 - s) f_i / factor + s f_i, s = (original / l_i - low) / (high - low).  No factor on cosines and sines.
 """
 from __future__ import annotations
 
@@ -49,6 +53,24 @@ def stretched_frequencies(theta: float, rotary_dim: int, stretch: dict):
     return out.astype(np.float32), 0.1 * math.log(factor) + 1.0
 
 
+def rescaled_frequencies(theta: float, rotary_dim: int, rescale: dict) -> np.ndarray:
+    """Inverse frequencies [rotary_dim/2] fp32 with the long waves slowed down; float64 on the host."""
+    factor, low, high, original = (float(rescale[k]) for k in ("factor", "low", "high", "original"))
+    if not (factor > 0 and original > 0 and low > 0 and high > low):
+        raise ValueError("rotary rescale: factor, original and low must be positive and high above low")
+    out = np.zeros(rotary_dim // 2, dtype=np.float64)
+    for i in range(rotary_dim // 2):
+        f = float(theta) ** (-2.0 * i / rotary_dim)
+        wave = 2.0 * math.pi / f
+        if wave > original / low:
+            f = f / factor
+        elif wave >= original / high:
+            s = (original / wave - low) / (high - low)
+            f = (1.0 - s) * f / factor + s * f
+        out[i] = f
+    return out.astype(np.float32)
+
+
 @register_position_encoding("rotary")
 class RotaryEmbedding(PositionEncoding):
     def __init__(self, params: dict, rt: Runtime):
@@ -64,8 +86,12 @@ class RotaryEmbedding(PositionEncoding):
         if not self.theta > 0:
             raise ValueError("rotary theta must be positive")
         magnitude = 1.0
+        if params.get("stretch") and params.get("rescale"):
+            raise ValueError("rotary: either stretch or rescale")
         if params.get("stretch"):
             inv, magnitude = stretched_frequencies(self.theta, self.rotary_dim, params["stretch"])
+        elif params.get("rescale"):
+            inv = rescaled_frequencies(self.theta, self.rotary_dim, params["rescale"])
         else:
             inv = inverse_frequencies(self.theta, self.rotary_dim, self.scale)
         self._table = RotaryTable(torch.from_numpy(inv).to(rt.device), self.rotary_dim,
