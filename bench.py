@@ -306,11 +306,18 @@ def step_timeline(session):
 # The Matidra sizes (post-norm layers; softmax attention whose values are the keys, then layers of gated attention behind
 # short convolutions beside a gated delta rule) stand beside a Qwen2 of the same width, layers, feed-forward width and
 # vocabulary whose heads are those of Matidra's attention layer.
+# The Fonuvik sizes (norms on both sides of every sublayer; layers of a token-shift recurrence alternating with layers of
+# attention in blocks of positions beside linear attention with a decay per key channel; routed experts with a shared
+# expert) stand beside the closest design that was here before, a Matidra of the same width, layers and vocabulary: its
+# parallel layers take the heads and widths of Fonuvik's two sides, and its dense feed-forward is as wide as what a
+# Fonuvik token runs (its chosen experts plus the shared one).
 DESIGN_SIZES = {
     "small": dict(gedalix="gedalix-small", layers=4),
     "16b-layers": dict(gedalix="gedalix-16b-layers", layers=4),
     "matidra-small": dict(matidra="matidra-small", layers=4),
     "matidra-3b-layers": dict(matidra="matidra-3b-layers", layers=4),
+    "fonuvik-small": dict(fonuvik="fonuvik-small", layers=4),
+    "fonuvik-3b-layers": dict(fonuvik="fonuvik-3b-layers", layers=4),
 }
 
 
@@ -333,6 +340,22 @@ def _equal_dense_matidra(raw, layers, max_positions):
                                       num_attention_heads=m["heads"], num_key_value_heads=m["kv_heads"], head_dim=m["dim"],
                                       intermediate_size=first["mlp"]["ff"], max_position_embeddings=max_positions, rope_theta=1e6,
                                       rms_norm_eps=1e-6, tie_word_embeddings=False))
+
+
+def _equal_matidra_fonuvik(raw, layers, max_positions):
+    from microllm_rocm_b200.config.matidra import MatidraConfig, attention_layer, parallel_layer
+    par = next(l for l in raw["layers"] if l["type"] == "parallel")
+    left, right, mlp = par["mixer"]["left"], par["mixer"]["right"], par["mlp"]
+    inter = mlp["router"]["top"] * mlp["expert"]["ff"] + (mlp["shared"]["ff"] if mlp.get("shared") else 0)
+    made = []
+    for layer in raw["layers"][:layers]:
+        if layer["type"] == "parallel":
+            made.append(parallel_layer(left["heads"], left["kv_heads"], left["dim"], left["vdim"], right["heads"], right["heads"],
+                                       right["dim"], right["vdim"], inter, conv=4, rank=right["a_rank"]))
+        else:
+            made.append(attention_layer(left["heads"], left["kv_heads"], left["dim"], inter, rot_dims=left["dim"] // 2))
+    return MatidraConfig.from_dict({"architecture": "Matidra", "vocab": raw["vocab"], "width": raw["width"], "norm": {"eps": 1e-6},
+                                    "postln_alpha": 2.0, "layers": made, "max_positions": max_positions})
 
 
 def _kernel_rows(step_fn, repeats=3):
@@ -370,7 +393,13 @@ def run_designs(args):
     for name in names:
         size = DESIGN_SIZES[name]
         layers = args.layers or size["layers"]
-        if "matidra" in size:
+        if "fonuvik" in size:
+            from microllm_rocm_b200.config.fonuvik import PRESETS as FONUVIK_PRESETS, FonuvikConfig
+            raw = copy.deepcopy(FONUVIK_PRESETS[size["fonuvik"]])
+            raw["layers"] = raw["layers"][:layers]
+            raw["max_positions"] = args.prompt + 512
+            designs = {"fonuvik": FonuvikConfig.from_dict(raw), "matidra": _equal_matidra_fonuvik(raw, layers, args.prompt + 512)}
+        elif "matidra" in size:
             from microllm_rocm_b200.config.matidra import PRESETS as MATIDRA_PRESETS, MatidraConfig
             raw = copy.deepcopy(MATIDRA_PRESETS[size["matidra"]])
             raw["layers"] = raw["layers"][:layers]
