@@ -32,6 +32,18 @@ struct Columns {               // a block of columns of fp32 rows, possibly K-sp
         for (int k = 1; k < n_partials; ++k) v += p[(size_t)k * partial_stride];
         return v;
     }
+    __device__ __forceinline__ float4 at4(long long row, int col) const {      // four columns, 16-byte aligned
+        const float* p = base + row * ld + col;
+        float4 v = *reinterpret_cast<const float4*>(p);
+        for (int k = 1; k < n_partials; ++k) {
+            const float4 w = *reinterpret_cast<const float4*>(p + (size_t)k * partial_stride);
+            v.x += w.x; v.y += w.y; v.z += w.z; v.w += w.w;
+        }
+        return v;
+    }
+    __host__ bool fours(int col) const {
+        return !base || (((uintptr_t)base % 16 == 0) && ld % 4 == 0 && col % 4 == 0 && (n_partials <= 1 || partial_stride % 4 == 0));
+    }
 };
 
 __device__ __forceinline__ float sigmoid(float v) {
@@ -182,6 +194,52 @@ __global__ void decay_prepare_kernel(PrepareParams p) {
     p.decay[t * p.HK + c] = p.form == 0 ? expf(log_sigmoid(z) * p.inv_tau) : expf(-expf(z));
 }
 
+// The same, four columns a thread (16-byte loads and stores): every block of columns starts and ends on a multiple of four.
+__global__ void decay_prepare_x4_kernel(PrepareParams p) {
+    pdl_prologue();
+    const int per_token = (3 * p.HK + p.HV) / 4;
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (long long)p.T * per_token) return;
+    const long long t = i / per_token;
+    int c = (int)(i % per_token) * 4;
+    if (c < p.HK) {
+        float4 q = p.q.at4(t, p.q_col + c);
+        q.x *= p.q_scale; q.y *= p.q_scale; q.z *= p.q_scale; q.w *= p.q_scale;
+        *reinterpret_cast<float4*>(p.q_out + t * p.HK + c) = q;
+        return;
+    }
+    c -= p.HK;
+    if (c < p.HK) { *reinterpret_cast<float4*>(p.k_out + t * p.HK + c) = p.k.at4(t, p.k_col + c); return; }
+    c -= p.HK;
+    if (c < p.HV) { *reinterpret_cast<float4*>(p.v_out + t * p.HV + c) = p.v.at4(t, p.v_col + c); return; }
+    c -= p.HV;
+    float z[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    if (p.pre.base) {
+        const float4 f = p.pre.at4(t, c);
+        z[0] = f.x; z[1] = f.y; z[2] = f.z; z[3] = f.w;
+    } else {
+        const float* w = p.w2 + (size_t)c * p.rank;
+        for (int r = 0; r < p.rank; ++r) {
+            float a = p.narrow.at(t, p.a_col + r);
+            if (p.narrow_act == 1) a = tanhf(a);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) z[j] = fmaf(w[(size_t)j * p.rank + r], a, z[j]);
+        }
+    }
+    if (p.bias) {
+        const float4 b = *reinterpret_cast<const float4*>(p.bias + c);
+        z[0] += b.x; z[1] += b.y; z[2] += b.z; z[3] += b.w;
+    }
+    float4 d;
+    if (p.form == 0) {
+        d.x = expf(log_sigmoid(z[0]) * p.inv_tau); d.y = expf(log_sigmoid(z[1]) * p.inv_tau);
+        d.z = expf(log_sigmoid(z[2]) * p.inv_tau); d.w = expf(log_sigmoid(z[3]) * p.inv_tau);
+    } else {
+        d.x = expf(-expf(z[0])); d.y = expf(-expf(z[1])); d.z = expf(-expf(z[2])); d.w = expf(-expf(z[3]));
+    }
+    *reinterpret_cast<float4*>(p.decay + t * p.HK + c) = d;
+}
+
 // ------------------------------------------------------------------------------ output norm and gate
 struct OutputParams {
     const float* o;                          // [T, H * DV]
@@ -220,6 +278,53 @@ __global__ void __launch_bounds__(WARPS * 32) head_norm_gate_kernel(OutputParams
             y *= p.gate_act == 1 ? g * sigmoid(g) : sigmoid(g);
         }
         dst[c] = from_f32<OutT>(y);
+    }
+}
+
+// The same, four columns a lane (16-byte loads of o and the gate, 8- or 16-byte stores): DV a multiple of four.
+template <typename OutT>
+__global__ void __launch_bounds__(WARPS * 32) head_norm_gate_x4_kernel(OutputParams p) {
+    constexpr int QUADS = MAX_D / 128;
+    pdl_prologue();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const long long item = (long long)blockIdx.x * WARPS + warp;
+    if (item >= (long long)p.T * p.H) return;
+    const int t = (int)(item / p.H), h = (int)(item % p.H);
+    const float* src = p.o + ((size_t)t * p.H + h) * p.DV;
+    float4 x[QUADS], g[QUADS];
+    float ss = 0.0f;
+#pragma unroll
+    for (int i = 0; i < QUADS; ++i) {
+        const int c = 4 * lane + 128 * i;
+        x[i] = c < p.DV ? *reinterpret_cast<const float4*>(src + c) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        if (p.gate.base && c < p.DV) g[i] = p.gate.at4(t, p.gate_col + h * p.DV + c);
+        ss = fmaf(x[i].x, x[i].x, ss); ss = fmaf(x[i].y, x[i].y, ss); ss = fmaf(x[i].z, x[i].z, ss); ss = fmaf(x[i].w, x[i].w, ss);
+    }
+    const float inv = 1.0f / sqrtf(warp_sum(ss) / (float)p.DV + p.eps);
+    OutT* dst = (OutT*)p.out + ((size_t)t * p.H + h) * p.DV;
+#pragma unroll
+    for (int i = 0; i < QUADS; ++i) {
+        const int c = 4 * lane + 128 * i;
+        if (c >= p.DV) continue;
+        float y[4] = {x[i].x * inv, x[i].y * inv, x[i].z * inv, x[i].w * inv};
+        if (p.weight) {
+            const float4 w = *reinterpret_cast<const float4*>(p.weight + (p.weight_per_head ? h * p.DV + c : c));
+            y[0] *= w.x; y[1] *= w.y; y[2] *= w.z; y[3] *= w.w;
+        }
+        if (p.gate.base) {
+            const float gs[4] = {g[i].x, g[i].y, g[i].z, g[i].w};
+#pragma unroll
+            for (int j = 0; j < 4; ++j) y[j] *= p.gate_act == 1 ? gs[j] * sigmoid(gs[j]) : sigmoid(gs[j]);
+        }
+        if constexpr (sizeof(OutT) == 4) {
+            *reinterpret_cast<float4*>(dst + c) = make_float4(y[0], y[1], y[2], y[3]);
+        } else {
+            uint2 raw;
+            OutT* v = reinterpret_cast<OutT*>(&raw);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) v[j] = from_f32<OutT>(y[j]);
+            *reinterpret_cast<uint2*>(dst + c) = raw;
+        }
     }
 }
 
@@ -286,7 +391,10 @@ MLB_EXPORT int mlb_decay_prepare(const float* q, long long q_ld, int q_partials,
                     cols(pre, pre_ld, pre_partials, pre_stride), bias, form, form == 0 ? 1.0f / tau : 0.0f, q_out, k_out, v_out, decay,
                     T, HK, HV};
     const long long n = (long long)T * (3 * HK + HV);
-    launch_kernel(decay_prepare_kernel, (unsigned)((n + 255) / 256), 256, 0, stream, p);
+    const bool fours = HK % 4 == 0 && HV % 4 == 0 && p.q.fours(q_col) && p.k.fours(k_col) && p.v.fours(v_col) && p.pre.fours(0) &&
+                       ((uintptr_t)q_out | (uintptr_t)k_out | (uintptr_t)v_out | (uintptr_t)decay | (uintptr_t)bias) % 16 == 0;
+    if (fours) launch_kernel(decay_prepare_x4_kernel, (unsigned)((n / 4 + 255) / 256), 256, 0, stream, p);
+    else launch_kernel(decay_prepare_kernel, (unsigned)((n + 255) / 256), 256, 0, stream, p);
     return check_launch("decay_prepare");
 }
 
@@ -300,7 +408,10 @@ MLB_EXPORT int mlb_head_norm_gate(const float* o, const float* weight, int weigh
                    gate_act, out, T, H, DV, eps};
     const long long items = (long long)T * H;
     const unsigned blocks = (unsigned)((items + WARPS - 1) / WARPS);
-    if (out_dtype == MLB_BF16) launch_kernel(head_norm_gate_kernel<__nv_bfloat16>, blocks, WARPS * 32, 0, stream, p);
+    const bool fours = DV % 4 == 0 && p.gate.fours(gate_col) && ((uintptr_t)o | (uintptr_t)weight | (uintptr_t)out) % 16 == 0;
+    if (fours && out_dtype == MLB_BF16) launch_kernel(head_norm_gate_x4_kernel<__nv_bfloat16>, blocks, WARPS * 32, 0, stream, p);
+    else if (fours && out_dtype == MLB_F32) launch_kernel(head_norm_gate_x4_kernel<float>, blocks, WARPS * 32, 0, stream, p);
+    else if (out_dtype == MLB_BF16) launch_kernel(head_norm_gate_kernel<__nv_bfloat16>, blocks, WARPS * 32, 0, stream, p);
     else if (out_dtype == MLB_F32) launch_kernel(head_norm_gate_kernel<float>, blocks, WARPS * 32, 0, stream, p);
     else return fail(MLB_INVALID_ARGUMENT, "head_norm_gate: unsupported dtype %d", out_dtype);
     return check_launch("head_norm_gate");
