@@ -119,7 +119,7 @@ struct ScanParams {
     int* error_flag;
 };
 
-constexpr int SCAN_COLS = 16;            // columns of S a CTA owns; its threads: SCAN_COLS * LANES
+constexpr int SCAN_COLS = 16;            // columns of S a CTA owns unless the kernel is told otherwise (COLS); its threads: COLS * LANES
 
 __device__ __forceinline__ void copy_async_f32(float* to_shared, const float* from, bool real) {
     const unsigned dst = (unsigned)__cvta_generic_to_shared(to_shared);
@@ -142,19 +142,19 @@ __device__ __forceinline__ void copy_async_f32x4(float* to_shared, const float* 
 // global memory inside a chunk.
 constexpr int RULE_DELTA = 0, RULE_DECAYED_SUM = 1, RULE_BONUS_READ = 2;
 
-template <int LANES, int ROWS, int CHUNK, int RULE>
-__global__ void __launch_bounds__(SCAN_COLS * LANES) delta_scan_kernel(ScanParams p) {
+template <int LANES, int ROWS, int CHUNK, int RULE, int COLS = SCAN_COLS>
+__global__ void __launch_bounds__(COLS * LANES) delta_scan_kernel(ScanParams p) {
     pdl_prologue();
-    constexpr int SCAN_LANES = LANES, SCAN_THREADS = SCAN_COLS * LANES;
+    constexpr int SCAN_LANES = LANES, SCAN_THREADS = COLS * LANES;
     constexpr int DKP = SCAN_LANES * ROWS;                    // padded key width
-    constexpr int PER_TOKEN = 3 * DKP + SCAN_COLS + 4;        // q | k | g | v of this CTA's columns | beta and three unused
+    constexpr int PER_TOKEN = 3 * DKP + COLS + 4;        // q | k | g | v of this CTA's columns | beta and three unused
     constexpr int STAGED = CHUNK * PER_TOKEN;
     __shared__ __align__(16) float stage_s[2][STAGED];
-    const int col_blocks = (p.DV + SCAN_COLS - 1) / SCAN_COLS;
+    const int col_blocks = (p.DV + COLS - 1) / COLS;
     const int cb = blockIdx.x % col_blocks, h = (blockIdx.x / col_blocks) % p.H, a = blockIdx.x / (col_blocks * p.H);
     const int part = threadIdx.x & (SCAN_LANES - 1);
     const int local_col = threadIdx.x / SCAN_LANES;
-    const int col = cb * SCAN_COLS + local_col;
+    const int col = cb * COLS + local_col;
     const bool col_ok = col < p.DV;
     const int start = p.seq_starts[a], n = p.seq_starts[a + 1] - start;
     const int slot = p.slots[a];
@@ -186,7 +186,7 @@ __global__ void __launch_bounds__(SCAN_COLS * LANES) delta_scan_kernel(ScanParam
     // tokens beyond the sequence's) becomes zero: a zero k and q keep such rows of S at zero whatever g is
     auto stage = [&](int first, int buf) {
         if (p.vec) {                             // every row a multiple of four floats and 16-byte aligned: four at a time
-            constexpr int UNITS = 3 * DKP / 4 + SCAN_COLS / 4 + 1;
+            constexpr int UNITS = 3 * DKP / 4 + COLS / 4 + 1;
             for (int e = threadIdx.x; e < CHUNK * UNITS; e += SCAN_THREADS) {
                 const int tok = e / UNITS, u = e % UNITS;
                 const bool live = first + tok < n;
@@ -198,11 +198,11 @@ __global__ void __launch_bounds__(SCAN_COLS * LANES) delta_scan_kernel(ScanParam
                     const float* at = (which == 0 ? q_base + t * qk_pitch : (which == 1 ? k_base + t * qk_pitch : g_base + t * g_pitch)) + (real ? c : 0);
                     copy_async_f32x4(to + which * DKP + c, at, live && real);
                 } else if (u < UNITS - 1) {
-                    const int c = (u - 3 * DKP / 4) * 4, vc = cb * SCAN_COLS + c;
+                    const int c = (u - 3 * DKP / 4) * 4, vc = cb * COLS + c;
                     const bool real = vc < p.DV;
                     copy_async_f32x4(to + 3 * DKP + c, v_base + t * p.ld_v + (real ? vc : 0), live && real);
                 } else {
-                    copy_async_f32(to + 3 * DKP + SCAN_COLS, b_base + t * p.H, live);
+                    copy_async_f32(to + 3 * DKP + COLS, b_base + t * p.H, live);
                 }
             }
             asm volatile("cp.async.commit_group;" ::: "memory");
@@ -213,14 +213,14 @@ __global__ void __launch_bounds__(SCAN_COLS * LANES) delta_scan_kernel(ScanParam
             const bool live = first + tok < n;
             const size_t t = live ? (size_t)(first + tok) : 0;
             const int which = w / DKP, c = w % DKP;
-            const int vc = cb * SCAN_COLS + (w - 3 * DKP);
+            const int vc = cb * COLS + (w - 3 * DKP);
             const float* at;
             bool real;
             if (which == 0) { real = c < p.DK; at = q_base + t * qk_pitch + (real ? c : 0); }
             else if (which == 1) { real = c < p.DK; at = k_base + t * qk_pitch + (real ? c : 0); }
             else if (which == 2) { real = c < p.DK; at = g_base + t * g_pitch + (real ? c : 0); }
-            else if (w < 3 * DKP + SCAN_COLS) { real = vc < p.DV; at = v_base + t * p.ld_v + (real ? vc : 0); }
-            else { real = w == 3 * DKP + SCAN_COLS; at = b_base + t * p.H; }
+            else if (w < 3 * DKP + COLS) { real = vc < p.DV; at = v_base + t * p.ld_v + (real ? vc : 0); }
+            else { real = w == 3 * DKP + COLS; at = b_base + t * p.H; }
             copy_async_f32(&stage_s[buf][e], at, live && real);
         }
         asm volatile("cp.async.commit_group;" ::: "memory");
@@ -232,12 +232,14 @@ __global__ void __launch_bounds__(SCAN_COLS * LANES) delta_scan_kernel(ScanParam
         if (first + CHUNK < n) stage(first + CHUNK, buf ^ 1);
         const int count = min(CHUNK, n - first);
         float* const o_at = p.o + ((size_t)start + first) * ((size_t)p.H * p.DV) + (size_t)h * p.DV + col;
-        auto token = [&](int tok) {
+        // `lone`: the lanes of a column meet for this token alone and its o is stored; else the lane's share of o is handed
+        // back and the lanes meet once for a group of tokens (below)
+        auto token = [&](int tok, bool lone) -> float {
             const float* row = stage_s[buf] + tok * PER_TOKEN;
             const float4* qs = reinterpret_cast<const float4*>(row) + part;
             const float4* ks = reinterpret_cast<const float4*>(row + DKP) + part;
             const float4* gs = reinterpret_cast<const float4*>(row + 2 * DKP) + part;
-            const float v = row[3 * DKP + local_col], beta = row[3 * DKP + SCAN_COLS];
+            const float v = row[3 * DKP + local_col], beta = row[3 * DKP + COLS];
             float4 kk[ROWS / 4];
             if (RULE != RULE_DELTA) {
                 // S <- diag(g) S + k v^T with the read-out S^T q behind it (decayed sum), or in front of it with the
@@ -260,12 +262,11 @@ __global__ void __launch_bounds__(SCAN_COLS * LANES) delta_scan_kernel(ScanParam
                     }
                 }
                 float out = (o0 + o1) + (o2 + o3);
-                out += __shfl_xor_sync(0xffffffffu, out, 1);
-                out += __shfl_xor_sync(0xffffffffu, out, 2);
-                out += __shfl_xor_sync(0xffffffffu, out, 4);
-                if (LANES == 16) out += __shfl_xor_sync(0xffffffffu, out, 8);
+                if (!lone) return out;
+#pragma unroll
+                for (int off = LANES / 2; off >= 1; off >>= 1) out += __shfl_xor_sync(0xffffffffu, out, off);
                 if (part == 0 && col_ok) o_at[(size_t)tok * ((size_t)p.H * p.DV)] = out;
-                return;
+                return 0.0f;
             }
             float d0 = 0.0f, d1 = 0.0f, d2 = 0.0f, d3 = 0.0f;          // four chains instead of one (always the same four)
 #pragma unroll
@@ -297,12 +298,43 @@ __global__ void __launch_bounds__(SCAN_COLS * LANES) delta_scan_kernel(ScanParam
             out += __shfl_xor_sync(0xffffffffu, out, 4);
             if (LANES == 16) out += __shfl_xor_sync(0xffffffffu, out, 8);
             if (part == 0 && col_ok) o_at[(size_t)tok * ((size_t)p.H * p.DV)] = out;
+            return 0.0f;
         };
-        if (count == CHUNK) {            // a whole chunk: unrolled, so that a token's read-out runs beside the next token's update
+        if (count == CHUNK && RULE != RULE_DELTA) {
+            // A whole chunk of a rule whose read-out nothing waits for: the lanes of a column keep their shares of o for a
+            // group of GROUP tokens and meet once for all of them.  A stage at distance `off` halves what a lane carries:
+            // it keeps the half of the group's tokens that its own bit `off` names and adds the partner's share of those,
+            // so that after the last stage lane `part` holds the whole o of token `part` of the group: GROUP - 1 shuffles
+            // for GROUP tokens instead of log2(LANES) each.  Every sum is the one the lone form makes (the same pairs at the
+            // same distances, largest first), so both forms give the same bits.
+            constexpr int GROUP = CHUNK < LANES ? CHUNK : LANES;
 #pragma unroll
-            for (int tok = 0; tok < CHUNK; ++tok) token(tok);
+            for (int g0 = 0; g0 < CHUNK; g0 += GROUP) {
+                float share[GROUP];
+#pragma unroll
+                for (int i = 0; i < GROUP; ++i) share[i] = token(g0 + i, false);
+#pragma unroll
+                for (int off = LANES / 2; off >= GROUP; off >>= 1) {
+#pragma unroll
+                    for (int i = 0; i < GROUP; ++i) share[i] += __shfl_xor_sync(0xffffffffu, share[i], off);
+                }
+#pragma unroll
+                for (int off = GROUP / 2; off >= 1; off >>= 1) {
+                    const bool upper = (part & off) != 0;
+#pragma unroll
+                    for (int i = 0; i < off; ++i) {
+                        const float keep = upper ? share[i + off] : share[i];
+                        const float send = upper ? share[i] : share[i + off];
+                        share[i] = keep + __shfl_xor_sync(0xffffffffu, send, off);
+                    }
+                }
+                if (part < GROUP && col_ok) o_at[(size_t)(g0 + part) * ((size_t)p.H * p.DV)] = share[0];
+            }
+        } else if (count == CHUNK) {     // a whole chunk: unrolled, so that a token's read-out runs beside the next token's update
+#pragma unroll
+            for (int tok = 0; tok < CHUNK; ++tok) token(tok, true);
         } else {
-            for (int tok = 0; tok < count; ++tok) token(tok);
+            for (int tok = 0; tok < count; ++tok) token(tok, true);
         }
         asm volatile("cp.async.wait_group 0;" ::: "memory");
         __syncthreads();
@@ -411,19 +443,19 @@ int launch_scan(const float* qn, const float* kn, const float* g, const float* b
     const bool aligned = ((uintptr_t)qn | (uintptr_t)kn | (uintptr_t)g | (uintptr_t)v) % 16 == 0;
     const int vec = aligned && DK % 4 == 0 && DV % 4 == 0 && ld_v % 4 == 0;
     ScanParams p{qn, kn, g, beta, bonus, v, ld_v, o, state, slots, num_slots, seq_starts, seq_pos0, A, H, G, DK, DV, vec, error_flag};
-    const unsigned blocks = (unsigned)((long long)A * H * ((DV + SCAN_COLS - 1) / SCAN_COLS));
     // A handful of long-running CTAs (a prompt portion: one CTA walks all its tokens) must be spread one to an SM.  Started
     // early behind a predecessor that still fills the SMs, they land wherever a slot falls free, several on one SM, and
     // the slowest SM decides: such a launch waits for its predecessor the plain way.  Many short CTAs (decoding) start early.
-    const bool early = blocks > 2u * (unsigned)sm_count();
-    auto go = [&](auto kernel, int lanes) {
-        if (early) launch_kernel(kernel, blocks, SCAN_COLS * lanes, 0, stream, p);
-        else kernel<<<blocks, SCAN_COLS * lanes, 0, stream>>>(p);
+    auto go = [&](auto kernel, int lanes, int cols) {
+        const unsigned blocks = (unsigned)((long long)A * H * ((DV + cols - 1) / cols));
+        const bool early = blocks > 2u * (unsigned)sm_count();
+        if (early) launch_kernel(kernel, blocks, cols * lanes, 0, stream, p);
+        else kernel<<<blocks, cols * lanes, 0, stream>>>(p);
     };
-    if (DK <= 32) go(delta_scan_kernel<8, 4, 16, RULE>, 8);
-    else if (DK <= 64) go(delta_scan_kernel<16, 4, 16, RULE>, 16);
-    else if (DK <= 128) go(delta_scan_kernel<16, 8, 8, RULE>, 16);
-    else go(delta_scan_kernel<16, 16, 4, RULE>, 16);
+    if (DK <= 32) go(delta_scan_kernel<8, 4, 16, RULE>, 8, SCAN_COLS);
+    else if (DK <= 64) go(delta_scan_kernel<16, 4, 16, RULE>, 16, SCAN_COLS);
+    else if (DK <= 128) go(delta_scan_kernel<16, 8, 8, RULE>, 16, SCAN_COLS);
+    else go(delta_scan_kernel<16, 16, 4, RULE>, 16, SCAN_COLS);
     return check_launch("scan");
 }
 
