@@ -139,4 +139,4 @@ def _ensure_builtin() -> None:
     global _loaded
     if not _loaded:
         _loaded = True
-        from ..models import fonuvik, gedalix, matidra, qwen2  # noqa: F401  (they register themselves)
+        from ..models import fonuvik, gedalix, lozepel, matidra, qwen2  # noqa: F401  (they register themselves)

@@ -1,7 +1,10 @@
 // Softmax attention whose keys and values may have different widths, with the steps that come between the
 // projections and the scores:
 //
-//   mlb_qk_prepare          per head: rms norm of q and k, each with a weight shared by the heads or with none (optional;
+//   mlb_row_norm_columns    sums the K-split partial results of a projection into plain fp32 rows and divides up to two
+//                           blocks of columns (all of q, all of k) by their root mean square over the WHOLE block,
+//                           times a weight of the block's length: a norm in front of the split into heads.
+//   mlb_qk_prepare          a bias per projection column (optional); per head: rms norm of q and k, each with a weight shared by the heads or with none (optional;
 //                           `norm_where` 1: in front of the rotation, 2: behind it), rotation of the first `rot_dims`
 //                           elements in interleaved pairs (2i, 2i + 1) by position * freq[i] with cos and sin times
 //                           `magnitude` (optional), q times 1 + coef * ln(floor((pos + 1) / every) + 1) (optional);
@@ -9,7 +12,10 @@
 //   mlb_paged_attention_kv  plain attention over those pages: one warp per (query token, query head), keys in tiles of
 //                           32 at absolute multiples of 32 with a running maximum and sum (the order of every addition
 //                           depends on the position alone, not on how the tokens were cut into steps), optional window,
-//                           optional output gate: o * sigmoid(gate) with the gate read from a projection's fp32 output.
+//                           optional output gate: o * sigmoid(gate) with the gate read from a projection's fp32 output
+//                           (one gate per element of a head, or one per head); optional cap on the scores,
+//                           s <- cap * tanh(s / cap); optional sink: exp(sink[head]) joins the softmax's denominator
+//                           (no key, no value, neither scaled nor capped).
 //
 // A page holds the keys of every kv head [NKV, page_size, DK] and behind them the values [NKV, page_size, DV].
 // Everything here is fp32 arithmetic; the inputs are fp32 columns of a projection's output (or K-split partial
@@ -49,6 +55,7 @@ struct PrepareParams {
     void* pages;
     int T, H, G, DK, DV;
     int PK, PV;                // widths of a stored query / key row and of a stored value row (>= DK, DV; the rest is zero)
+    const float* bias;         // one per column of the projection that q (and k, v when they share its rows) come from; null: none
     int* error_flag;
 };
 
@@ -74,7 +81,7 @@ __global__ void __launch_bounds__(WARPS * 32) qk_prepare_kernel(PrepareParams p)
 #pragma unroll
     for (int i = 0; i < NL; ++i) {
         const int c = lane + 32 * i;
-        x[i] = c < D ? src.at(t, col + c) : 0.0f;
+        x[i] = c < D ? src.at(t, col + c) + (p.bias ? p.bias[col + c] : 0.0f) : 0.0f;
     }
     // where the item goes
     KVT* page_row = nullptr;
@@ -145,8 +152,13 @@ struct AttnParams {
     int window;              // 0: all earlier keys
     float scale;
     Columns gate; int gate_col;      // gate.base null: no gate
+    int gate_per_head;               // 1: one gate per (token, head) at gate_col + head; 0: one per element at gate_col + head * dv + c
+    const float* sink;               // [heads] or null: exp(sink[head]) joins the denominator
+    float softcap;                   // > 0: s <- softcap * tanh(s / softcap)
     int* error_flag;
 };
+
+__device__ __forceinline__ float sigmoid_f32(float g) { return g >= 0.0f ? 1.0f / (1.0f + expf(-g)) : expf(g) / (1.0f + expf(g)); }
 
 template <typename QT, typename KVT, typename OutT>
 __global__ void __launch_bounds__(WARPS * 32) paged_attention_kv_kernel(AttnParams p) {
@@ -196,6 +208,7 @@ __global__ void __launch_bounds__(WARPS * 32) paged_attention_kv_kernel(AttnPara
             float dot = 0.0f;
             for (int c = 0; c < DK; ++c) dot = fmaf(q_s[warp][c], to_f32(krow[c]), dot);
             s = dot * p.scale;
+            if (p.softcap > 0.0f) s = p.softcap * tanhf(s / p.softcap);
         }
         const float m_new = fmaxf(m, warp_max(s));
         if (m_new == -INFINITY) continue;
@@ -219,16 +232,22 @@ __global__ void __launch_bounds__(WARPS * 32) paged_attention_kv_kernel(AttnPara
         }
     }
     OutT* orow = (OutT*)p.out + ((size_t)t * p.num_heads + h) * DV;
-    const float inv = l > 0.0f ? 1.0f / l : 0.0f;
+    float shrink = 1.0f;
+    if (p.sink) {
+        // the sink joins last: with m' = max(m, sink), l' = l * exp(m - m') + exp(sink - m') and the sums shrink alike
+        const float sk = p.sink[h];
+        const float m_new = fmaxf(m, sk);
+        shrink = (m == -INFINITY) ? 0.0f : expf(m - m_new);
+        l = l * shrink + expf(sk - m_new);
+    }
+    const float inv = l > 0.0f ? shrink / l : 0.0f;
+    const float head_gate = (p.gate.base && p.gate_per_head) ? sigmoid_f32(p.gate.at(t, p.gate_col + h)) : 1.0f;
 #pragma unroll
     for (int i = 0; i < PER_LANE; ++i) {
         const int c = lane + 32 * i;
         if (c < DV) {
             float o = acc[i] * inv;
-            if (p.gate.base) {
-                const float g = p.gate.at(t, p.gate_col + h * DV + c);
-                o *= g >= 0.0f ? 1.0f / (1.0f + expf(-g)) : expf(g) / (1.0f + expf(g));
-            }
+            if (p.gate.base) o *= p.gate_per_head ? head_gate : sigmoid_f32(p.gate.at(t, p.gate_col + h * DV + c));
             orow[c] = from_f32<OutT>(o);
         }
     }
@@ -237,7 +256,7 @@ __global__ void __launch_bounds__(WARPS * 32) paged_attention_kv_kernel(AttnPara
 // out[t, h * DV + c] = o[t, h * PV + c] * sigmoid(gate[t, gate_col + h * DV + c]): the heads' outputs taken out of rows
 // that are wider than a value (an attention kernel that ran on padded heads) and gated.  gate.base null: no gate.
 struct GateParams {
-    const void* o; void* out; Columns gate; int gate_col; int T, H, DV, PV;
+    const void* o; void* out; Columns gate; int gate_col; int T, H, DV, PV; int gate_per_head;
 };
 
 template <typename T>
@@ -249,20 +268,57 @@ __global__ void gate_heads_kernel(GateParams p) {
     const int c = (int)(i % p.DV), h = (int)((i / p.DV) % p.H);
     const long long t = i / ((long long)p.DV * p.H);
     float o = to_f32(((const T*)p.o)[(t * p.H + h) * p.PV + c]);
-    if (p.gate.base) {
-        const float g = p.gate.at(t, p.gate_col + h * p.DV + c);
-        o *= g >= 0.0f ? 1.0f / (1.0f + expf(-g)) : expf(g) / (1.0f + expf(g));
-    }
+    if (p.gate.base) o *= sigmoid_f32(p.gate.at(t, p.gate_per_head ? p.gate_col + h : p.gate_col + h * p.DV + c));
     ((T*)p.out)[i] = from_f32<T>(o);
+}
+
+// out[t, c] = sum of the partial results at (t, c); columns [col_a, col_a + n_a) and [col_b, col_b + n_b) are then divided by the
+// root mean square over their own block and multiplied by w_a / w_b (null: no weight).  n_b may be 0.  One CTA per row, a
+// fixed number of threads: a row's sums never depend on the batch.
+constexpr int ROW_NORM_THREADS = 256;
+__global__ void __launch_bounds__(ROW_NORM_THREADS)
+row_norm_columns_kernel(Columns src, int cols, int col_a, int n_a, const float* __restrict__ w_a, int col_b, int n_b,
+                        const float* __restrict__ w_b, float eps, float* __restrict__ out) {
+    pdl_prologue();
+    __shared__ float scratch[32];
+    const long long t = blockIdx.x;
+    float* row = out + (size_t)t * cols;
+    float ss_a = 0.0f, ss_b = 0.0f;
+    for (int c = threadIdx.x; c < cols; c += ROW_NORM_THREADS) {
+        const float v = src.at(t, c);
+        row[c] = v;
+        if (c >= col_a && c < col_a + n_a) ss_a = fmaf(v, v, ss_a);
+        if (c >= col_b && c < col_b + n_b) ss_b = fmaf(v, v, ss_b);
+    }
+    const float inv_a = 1.0f / sqrtf(block_sum(ss_a, scratch) / (float)n_a + eps);
+    const float inv_b = n_b > 0 ? 1.0f / sqrtf(block_sum(ss_b, scratch) / (float)n_b + eps) : 0.0f;
+    for (int c = threadIdx.x; c < cols; c += ROW_NORM_THREADS) {        // every thread rewrites only what it wrote itself
+        if (c >= col_a && c < col_a + n_a) row[c] = w_a ? row[c] * inv_a * w_a[c - col_a] : row[c] * inv_a;
+        else if (c >= col_b && c < col_b + n_b) row[c] = w_b ? row[c] * inv_b * w_b[c - col_b] : row[c] * inv_b;
+    }
 }
 
 }  // namespace
 
+MLB_EXPORT int mlb_row_norm_columns(const float* src, long long ld, int n_partials, long long partial_stride, int T, int cols,
+                                    int col_a, int n_a, const float* w_a, int col_b, int n_b, const float* w_b, float eps,
+                                    float* out, cudaStream_t stream) {
+    if (T < 0 || cols <= 0 || ld < cols || n_partials < 1 || n_a <= 0 || col_a < 0 || col_a + n_a > cols || n_b < 0 || col_b < 0 ||
+        col_b + n_b > cols || !src || !out)
+        return fail(MLB_INVALID_ARGUMENT, "row_norm_columns: bad sizes");
+    if (T == 0) return MLB_OK;
+    launch_kernel(row_norm_columns_kernel, (unsigned)T, ROW_NORM_THREADS, 0, stream, Columns{src, ld, n_partials, partial_stride}, cols,
+                  col_a, n_a, w_a, col_b, n_b, w_b, eps, out);
+    return check_launch("row_norm_columns");
+}
+
 MLB_EXPORT int mlb_gate_heads(const void* o, void* out, int dtype, const float* gate, long long gate_ld, int gate_partials,
-                              long long gate_partial_stride, int gate_col, int T, int H, int DV, int stored_v, cudaStream_t stream) {
+                              long long gate_partial_stride, int gate_col, int T, int H, int DV, int stored_v, int gate_per_head,
+                              cudaStream_t stream) {
     if (T < 0 || H <= 0 || DV <= 0 || stored_v < DV || !o || !out) return fail(MLB_INVALID_ARGUMENT, "gate_heads: bad operands");
     if (T == 0) return MLB_OK;
-    GateParams p{o, out, Columns{gate, gate_ld, gate_partials < 1 ? 1 : gate_partials, gate_partial_stride}, gate_col, T, H, DV, stored_v};
+    GateParams p{o, out, Columns{gate, gate_ld, gate_partials < 1 ? 1 : gate_partials, gate_partial_stride}, gate_col, T, H, DV, stored_v,
+                 gate_per_head ? 1 : 0};
     const long long n = (long long)T * H * DV;
     const unsigned blocks = (unsigned)((n + 255) / 256);
     if (dtype == MLB_BF16) launch_kernel(gate_heads_kernel<__nv_bfloat16>, blocks, 256, 0, stream, p);
@@ -277,7 +333,7 @@ MLB_EXPORT int mlb_qk_prepare(const float* src, long long ld, int n_partials, lo
                               float magnitude, float temp_coef, int temp_every, const int* positions, const int* token_seq,
                               const int* block_table, int max_blocks, int num_pages, int page_size, void* q_out, int q_dtype,
                               void* pages, int kv_dtype, int T, int H, int G, int DK, int DV, int stored_k, int stored_v,
-                              int* error_flag, cudaStream_t stream) {
+                              const float* bias, int* error_flag, cudaStream_t stream) {
     // `src` holds q (and k, v when kv_src is null); `kv_src`, when given, holds k and v (a projection that went through
     // another kernel first: the raw values of "values are the projected keys" come from the same place as k)
     if (T < 0 || H <= 0 || G <= 0 || H % G || DK <= 0 || DV <= 0 || DK > MAX_D || DV > MAX_D)
@@ -288,6 +344,7 @@ MLB_EXPORT int mlb_qk_prepare(const float* src, long long ld, int n_partials, lo
     if (rot_dims < 0 || rot_dims % 2 || rot_dims > DK) return fail(MLB_INVALID_ARGUMENT, "qk_prepare: rot_dims %d of %d", rot_dims, DK);
     if (pages && (page_size <= 0 || num_pages <= 0 || max_blocks <= 0 || !block_table))
         return fail(MLB_INVALID_ARGUMENT, "qk_prepare: bad cache geometry");
+    if (bias && kv_src) return fail(MLB_INVALID_ARGUMENT, "qk_prepare: a bias belongs to one projection's columns");
     if (T == 0) return MLB_OK;
     PrepareParams p{};
     p.q = Columns{src, ld, n_partials, partial_stride};
@@ -296,7 +353,7 @@ MLB_EXPORT int mlb_qk_prepare(const float* src, long long ld, int n_partials, lo
     p.q_norm = q_norm; p.k_norm = k_norm; p.eps = eps; p.norm_where = norm_where; p.freq = freq; p.rot_dims = rot_dims; p.magnitude = magnitude;
     p.temp_coef = temp_coef; p.temp_every = temp_every; p.positions = positions; p.token_seq = token_seq; p.block_table = block_table;
     p.max_blocks = max_blocks; p.num_pages = num_pages; p.page_size = page_size; p.q_out = q_out; p.pages = pages;
-    p.T = T; p.H = H; p.G = G; p.DK = DK; p.DV = DV; p.PK = stored_k; p.PV = stored_v; p.error_flag = error_flag;
+    p.T = T; p.H = H; p.G = G; p.DK = DK; p.DV = DV; p.PK = stored_k; p.PV = stored_v; p.bias = bias; p.error_flag = error_flag;
     const long long items = (long long)T * (H + 2 * G);
     const unsigned blocks = (unsigned)((items + WARPS - 1) / WARPS);
     const int kvd = pages ? kv_dtype : q_dtype;
@@ -322,7 +379,8 @@ MLB_EXPORT int mlb_paged_attention_kv(const void* q, int q_dtype, const void* pa
                                       const int* positions, const int* token_seq, const int* block_table, int max_blocks,
                                       int num_pages, int page_size, int tokens, int num_heads, int num_kv_heads, int dk, int dv,
                                       int window, int chunk, float scale, const float* gate, long long gate_ld, int gate_partials,
-                                      long long gate_partial_stride, int gate_col, int* error_flag, cudaStream_t stream) {
+                                      long long gate_partial_stride, int gate_col, int gate_per_head, const float* sink, float softcap,
+                                      int* error_flag, cudaStream_t stream) {
     if (tokens < 0 || num_heads <= 0 || num_kv_heads <= 0 || num_heads % num_kv_heads != 0)
         return fail(MLB_INVALID_ARGUMENT, "paged_attention_kv: bad head counts %d/%d", num_heads, num_kv_heads);
     if (dk <= 0 || dk > MAX_D || dv <= 0 || dv > MAX_D)
@@ -332,7 +390,8 @@ MLB_EXPORT int mlb_paged_attention_kv(const void* q, int q_dtype, const void* pa
     if (tokens == 0) return MLB_OK;
     AttnParams p{q, pages, out, positions, token_seq, block_table, max_blocks, num_pages, page_size, tokens, num_heads,
                  num_kv_heads, dk, dv, chunk, window, scale, Columns{gate, gate_ld, gate_partials < 1 ? 1 : gate_partials, gate_partial_stride},
-                 gate_col, error_flag};
+                 gate_col, gate_per_head ? 1 : 0, sink, softcap, error_flag};
+    if (softcap < 0.0f) return fail(MLB_INVALID_ARGUMENT, "paged_attention_kv: a cap on the scores is positive (0: none)");
     const long long items = (long long)tokens * num_heads;
     const unsigned blocks = (unsigned)((items + WARPS - 1) / WARPS);
     if (q_dtype == MLB_F32 && kv_dtype == MLB_F32 && out_dtype == MLB_F32)

@@ -12,6 +12,10 @@
 //                          form 0: sigmoid(z)^(1/tau) = exp(log_sigmoid(z) / tau);  form 1: exp(-exp(z)).
 //   mlb_head_norm_gate     o / sqrt(mean(o^2) + eps) per head, times a weight (one row of DV shared by the heads, or H * DV),
 //                          times act(gate) with the gate read from a projection's fp32 output (sigmoid or silu).
+//   mlb_lightning_prepare  what enters a recurrence with ONE fixed decay per head: q, k, v = silu of their projection columns
+//                          (fp32, partial results summed in split order) and the head's decay written for each of its key channels.
+//   mlb_row_norm_gate      o / sqrt(mean(o^2) + eps) over the WHOLE row (all heads together), times a weight of the row's length,
+//                          times sigmoid(gate) element by element.
 #include "common.cuh"
 
 using namespace mlb;
@@ -415,4 +419,78 @@ MLB_EXPORT int mlb_head_norm_gate(const float* o, const float* weight, int weigh
     else if (out_dtype == MLB_F32) launch_kernel(head_norm_gate_kernel<float>, blocks, WARPS * 32, 0, stream, p);
     else return fail(MLB_INVALID_ARGUMENT, "head_norm_gate: unsupported dtype %d", out_dtype);
     return check_launch("head_norm_gate");
+}
+
+namespace {
+
+__device__ __forceinline__ float silu_f32(float z) { return z / (1.0f + expf(-z)); }
+
+// one thread per element of q | k | v (HK + HK + HV per token)
+__global__ void lightning_prepare_kernel(Columns src, int q_col, int k_col, int v_col, const float* __restrict__ head_decay,
+                                         float* __restrict__ q_out, float* __restrict__ k_out, float* __restrict__ v_out,
+                                         float* __restrict__ decay, long long T, int HK, int HV, int DK) {
+    pdl_prologue();
+    const int per = 2 * HK + HV;
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= T * per) return;
+    const long long t = i / per;
+    const int c = (int)(i % per);
+    if (c < HK) {
+        q_out[t * HK + c] = silu_f32(src.at(t, q_col + c));
+        decay[t * HK + c] = head_decay[c / DK];
+    } else if (c < 2 * HK) {
+        k_out[t * HK + c - HK] = silu_f32(src.at(t, k_col + c - HK));
+    } else {
+        v_out[t * HV + c - 2 * HK] = silu_f32(src.at(t, v_col + c - 2 * HK));
+    }
+}
+
+constexpr int ROW_THREADS = 256;
+template <typename OutT>
+__global__ void __launch_bounds__(ROW_THREADS)
+row_norm_gate_kernel(const float* __restrict__ o, const float* __restrict__ weight, Columns gate, int gate_col, OutT* __restrict__ out,
+                     int width, float eps) {
+    pdl_prologue();
+    __shared__ float scratch[32];
+    const long long t = blockIdx.x;
+    const float* row = o + (size_t)t * width;
+    float ss = 0.0f;
+    for (int c = threadIdx.x; c < width; c += ROW_THREADS) ss = fmaf(row[c], row[c], ss);
+    const float inv = 1.0f / sqrtf(block_sum(ss, scratch) / (float)width + eps);
+    for (int c = threadIdx.x; c < width; c += ROW_THREADS) {
+        float v = row[c] * inv * (weight ? weight[c] : 1.0f);
+        if (gate.base) {
+            const float g = gate.at(t, gate_col + c);
+            v *= g >= 0.0f ? 1.0f / (1.0f + expf(-g)) : expf(g) / (1.0f + expf(g));
+        }
+        out[(size_t)t * width + c] = from_f32<OutT>(v);
+    }
+}
+
+}  // namespace
+
+MLB_EXPORT int mlb_lightning_prepare(const float* src, long long ld, int n_partials, long long partial_stride, int q_col, int k_col,
+                                     int v_col, const float* head_decay, float* q_out, float* k_out, float* v_out, float* decay,
+                                     int T, int H, int DK, int DV, cudaStream_t stream) {
+    if (T < 0 || H <= 0 || DK <= 0 || DV <= 0 || n_partials < 1 || !src || !head_decay || !q_out || !k_out || !v_out || !decay)
+        return fail(MLB_INVALID_ARGUMENT, "lightning_prepare: bad operands");
+    if (T == 0) return MLB_OK;
+    const long long n = (long long)T * (2LL * H * DK + (long long)H * DV);
+    launch_kernel(lightning_prepare_kernel, (unsigned)((n + 255) / 256), 256, 0, stream, Columns{src, ld, n_partials, partial_stride},
+                  q_col, k_col, v_col, head_decay, q_out, k_out, v_out, decay, (long long)T, H * DK, H * DV, DK);
+    return check_launch("lightning_prepare");
+}
+
+MLB_EXPORT int mlb_row_norm_gate(const float* o, const float* weight, const float* gate, long long gate_ld, int gate_partials,
+                                 long long gate_stride, int gate_col, void* out, int out_dtype, int T, int width, float eps,
+                                 cudaStream_t stream) {
+    if (T < 0 || width <= 0 || !o || !out) return fail(MLB_INVALID_ARGUMENT, "row_norm_gate: bad operands");
+    if (T == 0) return MLB_OK;
+    const Columns g{gate, gate_ld, gate_partials < 1 ? 1 : gate_partials, gate_stride};
+    if (out_dtype == MLB_BF16)
+        launch_kernel(row_norm_gate_kernel<__nv_bfloat16>, (unsigned)T, ROW_THREADS, 0, stream, o, weight, g, gate_col, (__nv_bfloat16*)out, width, eps);
+    else if (out_dtype == MLB_F32)
+        launch_kernel(row_norm_gate_kernel<float>, (unsigned)T, ROW_THREADS, 0, stream, o, weight, g, gate_col, (float*)out, width, eps);
+    else return fail(MLB_INVALID_ARGUMENT, "row_norm_gate: unsupported dtype %d", out_dtype);
+    return check_launch("row_norm_gate");
 }

@@ -71,6 +71,11 @@ def mma_sources(head_dim: int):
     return [("attention_mma.cu", {"HEAD_DIM": head_dim})] if head_dim % 32 == 0 and 32 <= head_dim <= MAX_HEAD_DIM else []
 
 
+def extras_supported(head_dim: int, softcap, sink: bool) -> bool:
+    """Whether the tensor-core kernels of one width take a cap on the scores and a sink in the denominator."""
+    return not softcap and not sink
+
+
 def tc_supported(head_dim: int, page_size: int, scale: float) -> bool:
     return (head_dim in TC_HEAD_DIMS and page_size % 8 == 0 and TC_KEYS_PER_TILE % page_size == 0
             and TC_KEYS_PER_TILE // page_size <= 16 and scale > 0.0)

@@ -26,6 +26,9 @@ ops.register_signatures("linear_attention.cu", {
                           c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
     "mlb_head_norm_gate": [c_void_p, c_void_p, c_int, c_void_p, c_longlong, c_int, c_longlong, c_int, c_int, c_void_p, c_int, c_int,
                            c_int, c_int, c_float, c_void_p],
+    "mlb_lightning_prepare": [c_void_p, c_longlong, c_int, c_longlong, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                              c_int, c_int, c_int, c_int, c_void_p],
+    "mlb_row_norm_gate": [c_void_p, c_void_p, c_void_p, c_longlong, c_int, c_longlong, c_int, c_void_p, c_int, c_int, c_int, c_float, c_void_p],
 })
 
 
@@ -111,3 +114,44 @@ def head_norm_gate(o: torch.Tensor, weight: Optional[torch.Tensor], gate, gate_c
     L = ops.lib("linear_attention.cu")
     build.check(L, L.mlb_head_norm_gate(o.data_ptr(), ops._ptr(weight), per_head, g_ptr, g_ld, g_n, g_stride, int(gate_col),
                                         GATE_ACTS[gate_act], out.data_ptr(), ops.dtype_tag(out), T, heads, dv, float(eps), ops._stream()))
+
+
+def lightning_prepare(proj, q_col: int, k_col: int, v_col: int, head_decay: torch.Tensor, q_out: torch.Tensor, k_out: torch.Tensor,
+                      v_out: torch.Tensor, decay: torch.Tensor, heads: int, dk: int, dv: int) -> None:
+    """q_out, k_out [T, heads * dk], v_out [T, heads * dv] = silu of the column blocks of `proj` (fp32 rows or partial results)
+    from q_col, k_col, v_col; decay [T, heads * dk] = head_decay[head] (fp32 [heads]) for every key channel of the head."""
+    _, ld, n, stride = _columns(proj, "proj")
+    T = proj.shape[-2]
+    ops._need(head_decay, "head_decay", torch.float32, 1)
+    for name, t, shape in (("q_out", q_out, (T, heads * dk)), ("k_out", k_out, (T, heads * dk)), ("decay", decay, (T, heads * dk)),
+                           ("v_out", v_out, (T, heads * dv))):
+        ops._need(t, name, torch.float32, 2)
+        if tuple(t.shape) != shape:
+            raise KernelError(f"lightning_prepare: {name} must be {shape}")
+    if head_decay.shape[0] != heads or max(q_col, k_col) + heads * dk > ld or v_col + heads * dv > ld:
+        raise KernelError("lightning_prepare: shapes do not agree")
+    L = ops.lib("linear_attention.cu")
+    build.check(L, L.mlb_lightning_prepare(proj.data_ptr(), ld, n, stride, int(q_col), int(k_col), int(v_col), head_decay.data_ptr(),
+                                           q_out.data_ptr(), k_out.data_ptr(), v_out.data_ptr(), decay.data_ptr(), T, heads, dk, dv, ops._stream()))
+
+
+def row_norm_gate(o: torch.Tensor, weight: Optional[torch.Tensor], gate, gate_col: int, out: torch.Tensor, eps: float) -> None:
+    """out = o / rms(o) over the whole row * weight * sigmoid(gate columns from gate_col) in out's dtype; `weight` [width] fp32
+    or None; `gate` fp32 rows or partial results, or None."""
+    ops._need(o, "o", torch.float32, 2); ops._need(out, "out", dims=2)
+    T, width = o.shape
+    if tuple(out.shape) != (T, width):
+        raise KernelError("row_norm_gate: shapes do not agree")
+    if weight is not None:
+        ops._need(weight, "weight", torch.float32, 1)
+        if weight.shape[0] != width:
+            raise KernelError("row_norm_gate: the weight has the row's length")
+    g_ptr, g_ld, g_n, g_stride = None, 0, 1, 0
+    if gate is not None:
+        _, g_ld, g_n, g_stride = _columns(gate, "gate")
+        g_ptr = gate.data_ptr()
+        if gate_col + width > g_ld:
+            raise KernelError("row_norm_gate: the gate has no such columns")
+    L = ops.lib("linear_attention.cu")
+    build.check(L, L.mlb_row_norm_gate(o.data_ptr(), ops._ptr(weight), g_ptr, g_ld, g_n, g_stride, int(gate_col), out.data_ptr(),
+                                       ops.dtype_tag(out), T, width, float(eps), ops._stream()))

@@ -166,7 +166,16 @@ class NormedAttention(Mixer):
       q times 1 + coef * ln(floor((p + 1) / every) + 1) at position p (`q_temp = (coef, every)`)
       score = q . k * scale, causal (optionally the last `window` keys; optionally only the keys of the query's own
           block of `chunk` positions, blocks counted from position 0 of the sequence), softmax
-      concat_heads(o) * sigmoid(Wg x) (`gate`), then Wo
+      concat_heads(o) * sigmoid(Wg x) (`gate`; `gate="head"`: Wg has one row per head and a head's whole output is multiplied
+          by its one number), then Wo
+
+    Further options: `bias` (q and k projections have biases, added as the projection is read; values that are the projected
+    keys carry the key's bias), `qk_norm="row"` (q and k are each divided by the root mean square of their WHOLE projection
+    row, before the split into heads, times a weight of the row's length), `softcap` (score <- cap * tanh(score / cap)),
+    `sink` ("learned": one number per head whose exponential joins the softmax's denominator, with no key and no value,
+    neither scaled nor capped; "zero": the same with the number fixed at 0, i.e. 1 is added to the denominator), and
+    `kv_shared` (the layer has no key and value projections of its own: its run reads the pages another run wrote, with its
+    own queries).
 
     Keys have `dim` elements per head and values `vdim`; the cache holds both widths (`PagedKVNeed.value_dim`).  All
     projections that read x are one fused product; norm, rotation, temperature, softmax and the gate are fp32.
@@ -184,7 +193,15 @@ class NormedAttention(Mixer):
         self.values = params.get("values", "projected")
         self.taps = int(params.get("conv", 1))
         self.has_gate = bool(params.get("gate", False))
-        self.qk_norm = bool(params.get("qk_norm", True))
+        self.gate_per_head = params.get("gate") == "head"
+        self.row_norm = params.get("qk_norm") == "row"
+        self.qk_norm = bool(params.get("qk_norm", True)) and not self.row_norm
+        self.has_bias = bool(params.get("bias", False))
+        self.softcap = float(params["softcap"]) if params.get("softcap") else None
+        self.sink_kind = params.get("sink")
+        if self.sink_kind not in (None, "learned", "zero"):
+            raise ValueError(f"normed_attention: sink {self.sink_kind!r} is not 'learned' or 'zero'")
+        self.kv_shared = bool(params.get("kv_shared", False))
         self.q_temp = tuple(params["q_temp"]) if params.get("q_temp") else None
         self.window = params.get("window")
         self.chunk = int(params["chunk"]) if params.get("chunk") else None
@@ -201,9 +218,13 @@ class NormedAttention(Mixer):
         if self.nh % self.nkv:
             raise ValueError("num_heads must be a multiple of num_kv_heads")
         attention_kv.check_widths(self.dk, self.dv)
+        if self.kv_shared and (self.taps > 1 or self.values == "keys"):
+            raise ValueError("normed_attention: a layer that reads another layer's keys and values has no convolution and no value rule of its own")
+        if self.has_bias and self.taps > 1:
+            raise ValueError("normed_attention: biases and a convolution do not go together")
         names = dict(q="q_proj.weight", k="k_proj.weight", v="v_proj.weight", o="o_proj.weight", q_norm="q_norm.weight",
                      k_norm="k_norm.weight", gate="g_proj.weight", q_conv="q_conv.weight", k_conv="k_conv.weight",
-                     v_conv="v_conv.weight")
+                     v_conv="v_conv.weight", q_bias="q_proj.bias", k_bias="k_proj.bias", sink="sink")
         names.update(params.get("names", {}))
         self.names = names
         self.rt = rt
@@ -214,9 +235,9 @@ class NormedAttention(Mixer):
         self.rot_dims = table.rotary_dim if table is not None else 0
         self.magnitude = table.magnitude if table is not None else 1.0
         # columns of the fused input projection: q | k | v (if projected) | gate (if any)
-        self.q_cols, self.k_cols = self.nh * self.dk, self.nkv * self.dk
-        self.v_cols = self.nkv * self.dv if self.values == "projected" else 0
-        self.g_cols = self.nh * self.dv if self.has_gate else 0
+        self.q_cols, self.k_cols = self.nh * self.dk, (0 if self.kv_shared else self.nkv * self.dk)
+        self.v_cols = self.nkv * self.dv if self.values == "projected" and not self.kv_shared else 0
+        self.g_cols = (self.nh if self.gate_per_head else self.nh * self.dv) if self.has_gate else 0
         self.conv_cols = self.q_cols + self.k_cols + self.v_cols
         # bf16: the attention itself runs on the tensor-core kernels of equal key and value widths; unequal widths are
         # stored with zeros up to one width that those kernels take (the plain kernel with the true widths otherwise,
@@ -224,7 +245,11 @@ class NormedAttention(Mixer):
         self.stored = None
         if not rt.is_fp32:
             self.stored = next((w for w in SHARED_KERNEL_WIDTHS if w >= max(self.dk, self.dv)), None)
-        self.w_in = self.w_o = self.q_norm_w = self.k_norm_w = self.w_conv = None
+        if self.stored is not None and not attention_kernels.extras_supported(self.stored, self.softcap, self.sink_kind is not None):
+            self.stored = None           # a cap or a sink that the kernels of one width do not take: the plain kernel
+        self.w_in = self.w_o = self.q_norm_w = self.k_norm_w = self.w_conv = self.b_in = self.sink = None
+        # rows of the fused projection; a gate of one row per head is padded to a multiple of 8 rows, which the products like
+        self.in_rows = -(-(self.conv_cols + self.g_cols) // 8) * 8 if self.gate_per_head else self.conv_cols + self.g_cols
 
     # --- declarations -----------------------------------------------------------------
     def cache_need(self):
@@ -236,7 +261,7 @@ class NormedAttention(Mixer):
 
     def _pieces(self):
         n = self.names
-        pieces = [(n["q"], 0), (n["k"], self.q_cols)]
+        pieces = [(n["q"], 0)] + ([] if self.kv_shared else [(n["k"], self.q_cols)])
         if self.v_cols:
             pieces.append((n["v"], self.q_cols + self.k_cols))
         if self.has_gate:
@@ -245,8 +270,19 @@ class NormedAttention(Mixer):
 
     def weight_specs(self) -> Dict[str, WeightSpec]:
         n = self.names
-        specs = {n["q"]: WeightSpec((self.q_cols, self.hidden)), n["k"]: WeightSpec((self.k_cols, self.hidden)),
-                 n["o"]: WeightSpec((self.hidden, self.nh * self.dv))}
+        specs = {n["q"]: WeightSpec((self.q_cols, self.hidden)), n["o"]: WeightSpec((self.hidden, self.nh * self.dv))}
+        if not self.kv_shared:
+            specs[n["k"]] = WeightSpec((self.k_cols, self.hidden))
+        if self.has_bias:
+            specs[n["q_bias"]] = WeightSpec((self.q_cols,), role="vector", init=("normal", 0.1))
+            if not self.kv_shared:
+                specs[n["k_bias"]] = WeightSpec((self.k_cols,), role="vector", init=("normal", 0.1))
+        if self.row_norm:
+            specs[n["q_norm"]] = WeightSpec((self.q_cols,), role="vector", init=("one_plus_normal", 0.1))
+            if not self.kv_shared:
+                specs[n["k_norm"]] = WeightSpec((self.k_cols,), role="vector", init=("one_plus_normal", 0.1))
+        if self.sink_kind == "learned":
+            specs[n["sink"]] = WeightSpec((self.nh,), role="vector", init=("normal", 1.0))
         if self.v_cols:
             specs[n["v"]] = WeightSpec((self.v_cols, self.hidden))
         if self.has_gate:
@@ -261,7 +297,11 @@ class NormedAttention(Mixer):
         return specs
 
     def fused_tensors(self):
-        fused = {"in_proj.weight": (WeightSpec((self.conv_cols + self.g_cols, self.hidden)), self._pieces())}
+        fused = {"in_proj.weight": (WeightSpec((self.in_rows, self.hidden)), self._pieces())}
+        if self.has_bias:
+            n = self.names
+            fused["in_proj.bias"] = (WeightSpec((self.in_rows,), role="vector"),
+                                     [(n["q_bias"], 0)] + ([] if self.kv_shared else [(n["k_bias"], self.q_cols)]))
         if self.taps > 1:
             n = self.names
             rows = [(n["q_conv"], 0), (n["k_conv"], self.q_cols)] + ([(n["v_conv"], self.q_cols + self.k_cols)] if self.v_cols else [])
@@ -280,10 +320,31 @@ class NormedAttention(Mixer):
 
     def bind(self, tensors):
         n = self.names
+        used = self.conv_cols + self.g_cols
         if "in_proj.weight" in tensors:
             self.w_in = tensors["in_proj.weight"]
+            self.w_in[used:].zero_()                     # the padding rows: their columns of the product are never read
         else:
-            self.w_in = torch.cat([tensors[name] for name, _ in self._pieces()], 0).contiguous()
+            pieces = [tensors[name] for name, _ in self._pieces()]
+            if self.in_rows > used:
+                pieces.append(torch.zeros((self.in_rows - used, self.hidden), dtype=pieces[0].dtype, device=pieces[0].device))
+            self.w_in = torch.cat(pieces, 0).contiguous()
+        if self.has_bias:
+            if "in_proj.bias" in tensors:
+                self.b_in = tensors["in_proj.bias"]
+                self.b_in[self.q_cols + self.k_cols:].zero_()           # only q and k have biases
+            else:
+                self.b_in = torch.zeros((self.in_rows,), dtype=torch.float32, device=self.w_in.device)
+                self.b_in[:self.q_cols] = tensors[n["q_bias"]]
+                if not self.kv_shared:
+                    self.b_in[self.q_cols:self.q_cols + self.k_cols] = tensors[n["k_bias"]]
+        if self.sink_kind == "learned":
+            self.sink = tensors[n["sink"]]
+        elif self.sink_kind == "zero":
+            self.sink = torch.zeros((self.nh,), dtype=torch.float32, device=self.w_in.device)
+        if self.row_norm:
+            self.q_norm_w = tensors[n["q_norm"]]
+            self.k_norm_w = None if self.kv_shared else tensors[n["k_norm"]]
         if self.taps > 1:
             if "conv.weight" in tensors:
                 self.w_conv = tensors["conv.weight"]
@@ -291,18 +352,20 @@ class NormedAttention(Mixer):
                 keys = ["q_conv", "k_conv"] + (["v_conv"] if self.v_cols else [])
                 self.w_conv = torch.cat([tensors[n[k]] for k in keys], 0).contiguous()
         self.w_o = tensors[n["o"]]
-        self.q_norm_w = tensors[n["q_norm"]] if self.qk_norm and self.norm_weight else None
-        self.k_norm_w = tensors[n["k_norm"]] if self.qk_norm and self.norm_weight else None
+        if not self.row_norm:
+            self.q_norm_w = tensors[n["q_norm"]] if self.qk_norm and self.norm_weight else None
+            self.k_norm_w = tensors[n["k_norm"]] if self.qk_norm and self.norm_weight else None
 
     def replay_key(self):
         if not self.rt.is_fp32 and not gemm_bf16._direct_library(self.rt.device):
             return None
         rotary = None if self.freq is None else (self.freq.data_ptr(), self.rot_dims, self.magnitude)
         return ("normed_attention", self.hidden, self.nh, self.nkv, self.dk, self.dv, self.scale, self.eps, self.values, self.taps,
-                self.has_gate, self.qk_norm, self.norm_weight, self.norm_where, self.q_temp, self.window, self.chunk, rotary)
+                self.has_gate, self.qk_norm, self.norm_weight, self.norm_where, self.q_temp, self.window, self.chunk, rotary,
+                self.gate_per_head, self.row_norm, self.has_bias, self.softcap, self.sink_kind, self.kv_shared)
 
     def own_tensors(self):
-        return [self.w_in, self.w_o, self.q_norm_w, self.k_norm_w, self.w_conv]
+        return [self.w_in, self.w_o, self.q_norm_w, self.k_norm_w, self.w_conv, self.b_in, self.sink if self.sink_kind == "learned" else None]
 
     def _shared_kernels(self, page_size: int) -> bool:
         """Whether the attention itself runs on the kernels of equal key and value widths."""
@@ -327,6 +390,11 @@ class NormedAttention(Mixer):
                       alloc=lambda shape, dtype: ctx.buffer("normed_attention.proj", shape, dtype))
         src, q_col, k_col = proj, 0, self.q_cols
         v_col = self.q_cols + self.k_cols if self.v_cols else k_col
+        if self.row_norm:
+            # q and k divided by the root mean square of their whole rows; the partial results become plain rows on the way
+            src = ctx.buffer("normed_attention.rows", (T, self.in_rows), torch.float32)
+            attention_kv.row_norm_columns(proj, src, 0, self.q_cols, self.q_norm_w, self.q_cols, self.k_cols, self.k_norm_w, self.eps)
+            proj = src
         if self.taps > 1:
             state = cache["conv"]
             src = ctx.buffer("normed_attention.conv", (T, self.conv_cols), torch.float32)
@@ -334,12 +402,13 @@ class NormedAttention(Mixer):
         sk = self.stored or self.dk
         sv = self.stored or self.dv
         q = ctx.buffer("normed_attention.q", (T, self.nh * sk), dt)
-        attention_kv.qk_prepare(src, q_col, k_col, v_col, q_norm=self.q_norm_w, k_norm=self.k_norm_w, eps=self.eps, freq=self.freq,
+        head_norms = (None, None) if self.row_norm else (self.q_norm_w, self.k_norm_w)       # the rows' norm has been applied above
+        attention_kv.qk_prepare(src, q_col, k_col, v_col, q_norm=head_norms[0], k_norm=head_norms[1], eps=self.eps, freq=self.freq,
                                 rot_dims=self.rot_dims, magnitude=self.magnitude, q_temp=self.q_temp, positions=ctx.positions,
                                 token_seq=ctx.token_seq, block_table=kv_view.block_table,
-                                pages=kv_view.pages if kv_view.writable else None, page_size=kv_view.page_size, q_out=q,
+                                pages=kv_view.pages if kv_view.writable and not self.kv_shared else None, page_size=kv_view.page_size, q_out=q,
                                 heads=self.nh, kv_heads=self.nkv, dk=self.dk, dv=self.dv, error_flag=flag, stored=self.stored,
-                                norm=self.norm_where if self.qk_norm else None)
+                                norm=self.norm_where if self.qk_norm else None, bias=self.b_in)
         o = ctx.buffer("normed_attention.o", (T, self.nh * self.dv), dt)
         gate = proj if self.has_gate else None
         if self._shared_kernels(kv_view.page_size):
@@ -347,15 +416,15 @@ class NormedAttention(Mixer):
             attention_kernels.paged_attention(q, kv_view.pages, wide, ctx, kv_view.block_table, self.nh, self.nkv, sk, self.scale,
                                               self.window, beside_mma_products=gemm_bf16.gemv_preferred(x, self.w_o), chunk=self.chunk)
             if wide is not o:
-                attention_kv.gate_heads(wide, o, gate, self.conv_cols, self.nh, self.dv, sv)
+                attention_kv.gate_heads(wide, o, gate, self.conv_cols, self.nh, self.dv, sv, per_head=self.gate_per_head)
         elif self.stored is not None:            # a page size the tensor-core kernels do not take: the plain kernel of one width
             wide = ctx.buffer("normed_attention.o_stored", (T, self.nh * sv), dt)
             attention_kernels.paged_attention(q, kv_view.pages, wide, ctx, kv_view.block_table, self.nh, self.nkv, sk, self.scale, self.window,
                                               chunk=self.chunk)
-            attention_kv.gate_heads(wide, o, gate, self.conv_cols, self.nh, self.dv, sv)
+            attention_kv.gate_heads(wide, o, gate, self.conv_cols, self.nh, self.dv, sv, per_head=self.gate_per_head)
         else:
             attention_kv.paged_attention_kv(q, kv_view.pages, o, ctx.positions, ctx.token_seq, kv_view.block_table, kv_view.page_size,
                                             self.nh, self.nkv, self.dk, self.dv, self.scale, self.window, gate, self.conv_cols, flag,
-                                            chunk=self.chunk)
+                                            chunk=self.chunk, gate_per_head=self.gate_per_head, sink=self.sink, softcap=self.softcap or 0.0)
         return linear(o, self.w_o, None, torch.float32, partials_ok=True, error_flag=flag,
                       alloc=lambda shape, dtype: ctx.buffer("normed_attention.out", shape, dtype))

@@ -166,6 +166,7 @@ class SandwichResidualBlock(Block):
         self.prefix = params.get("prefix", "")
         self.size, self.eps = int(params["size"]), float(params["eps"])
         self.post_names = tuple(params.get("post_names", ("post_mixer_norm.weight", "post_ffn_norm.weight")))
+        self.one_plus = bool(params.get("one_plus", False))      # the two weights behind the sublayers are stored minus one
         self.mixer_norm, self.mixer, self.ffn_norm, self.feed_forward = mixer_norm, mixer, ffn_norm, feed_forward
         self.has_ff = not getattr(feed_forward, "absent", False)
         if self.has_ff and not (hasattr(ffn_norm, "weight") and getattr(ffn_norm, "eps", None) == self.eps and hasattr(ffn_norm, "size")):
@@ -175,14 +176,16 @@ class SandwichResidualBlock(Block):
 
     def weight_specs(self) -> Dict[str, WeightSpec]:
         names = self.post_names if self.has_ff else self.post_names[:1]
-        return {n: WeightSpec((self.size,), role="vector", init=("one_plus_normal", 0.1)) for n in names}
+        init = ("normal", 0.1) if self.one_plus else ("one_plus_normal", 0.1)
+        return {n: WeightSpec((self.size,), role="vector", init=init) for n in names}
 
     def kernel_sources(self):
         return [("post_norm.cu", {})]
 
     def bind(self, tensors):
-        self.w_post1 = tensors[self.post_names[0]]
-        self.w_post2 = tensors[self.post_names[1]] if self.has_ff else None
+        take = (lambda t: (t.to(torch.float32) + 1.0).contiguous()) if self.one_plus else (lambda t: t)
+        self.w_post1 = take(tensors[self.post_names[0]])
+        self.w_post2 = take(tensors[self.post_names[1]]) if self.has_ff else None
 
     def replay_key(self):
         keys = [p.replay_key() for p in (self.mixer_norm, self.mixer, self.ffn_norm, self.feed_forward)]

@@ -65,6 +65,12 @@ class Model:
         self._keep_embedding = any(e is not None and e.needs_embedding for e in self.run_entries)
         # caches: one entry per owning run
         self.cache_entries: Dict[str, CacheEntry] = {}
+        # what the embedding keeps per sequence between steps (the token in front of the next one), if anything
+        self.embedding_cache: Optional[str] = None
+        embedding_need = self.embedding.cache_need() if hasattr(self.embedding, "cache_need") else None
+        if embedding_need is not None:
+            self.embedding_cache = "embedding"
+            self.cache_entries[self.embedding_cache] = CacheEntry(self.embedding_cache, embedding_need)
         self.run_cache: List[Tuple[Optional[str], bool]] = []    # per run: (cache name, owns it)
         self.run_cache_parts: Dict[str, List[str]] = {}          # cache name of a run whose mixer keeps several caches -> sub-names
         for i, run in enumerate(spec.order):
@@ -201,7 +207,10 @@ class Model:
         if not self.bound:
             raise RuntimeError("model weights are not bound")
         ctx.step_values.clear()              # nothing computed from an earlier step's positions or tokens survives
-        residual = self.embedding.forward(ctx.token_ids)
+        if self.embedding_cache is not None:
+            residual = self.embedding.forward(ctx.token_ids, ctx, caches[self.embedding_cache])
+        else:
+            residual = self.embedding.forward(ctx.token_ids)
         self.position.on_embedding(residual, ctx)
         delta = None
         sink = ctx.tensor_sink

@@ -15,6 +15,12 @@ grows with the tokens):
   per head:  o_t = (S + diag(u) k_t v_t^T)^T r_t  (the bonus u for the present token only);  then S <- diag(w_t) S + k_t v_t^T
   o / rms(o) per head * weight (heads x dim) * gate,  then Wo.  The previous token's x is part of the state.
 
+`lightning_attention`
+  q, k = silu(Wq x), silu(Wk x)  (heads x dim),  v = silu(Wv x)  (heads x vdim);  one FIXED decay per head, a constant d_h
+  per head, S [dim, vdim] from zero:  S <- d_h S + k_t v_t^T;  o_t = S^T q_t  (no other scale)
+  the heads side by side are divided by their root mean square TOGETHER, times a weight of heads x vdim, times
+  sigmoid(Wg x) element by element, then Wo.  q, k, v and the gate are one fused product.
+
 The second step of the narrow projection (Wa2, Ww2) runs as a product when its inner width suits the product kernels
 (a multiple of 8), else inside the kernel that needs its result, in fp32.  Decays, their exponentials, the recurrence,
 its state and the output norm are fp32 whatever the compute dtype.
@@ -120,6 +126,80 @@ class GatedLinearAttention(Mixer):
         recurrent.linear_scan("decayed_sum", q, k, decay, v, o, state.storage, state.slots, ctx, self.nh, self.dk, self.dv)
         gated = buf("gated", (T, self.v_cols), self.rt.dtype)
         linear_attention.head_norm_gate(o, self.norm_w, proj, self.g_col, "silu", gated, self.nh, self.dv, self.eps)
+        return linear(gated, self.w_o, None, f32, partials_ok=True, error_flag=flag, alloc=lambda shape, dtype: buf("out", shape, dtype))
+
+
+@register_mixer("lightning_attention")
+class LightningAttention(Mixer):
+    graph_safe = True
+
+    def __init__(self, params: dict, rt: Runtime, position: Optional[PositionEncoding] = None):
+        self.prefix = params.get("prefix", "")
+        self.hidden = int(params["hidden_size"])
+        self.nh = int(params["num_heads"])
+        self.dk, self.dv = int(params["dim"]), int(params["vdim"])
+        self.decay_values = tuple(float(d) for d in params["decay"])
+        self.eps = float(params.get("eps", 1e-6))
+        _check_widths("lightning_attention", self.dk, self.dv)
+        if len(self.decay_values) != self.nh:
+            raise ValueError("lightning_attention: one decay per head")
+        names = dict(q="q_proj.weight", k="k_proj.weight", v="v_proj.weight", gate="g_proj.weight", o="o_proj.weight", norm="o_norm.weight")
+        names.update(params.get("names", {}))
+        self.names = names
+        self.rt = rt
+        # columns of the fused input projection: q | k | v | gate
+        self.qk_cols, self.v_cols = self.nh * self.dk, self.nh * self.dv
+        self.k_col, self.v_col = self.qk_cols, 2 * self.qk_cols
+        self.g_col = self.v_col + self.v_cols
+        self.in_rows = self.g_col + self.v_cols
+        self.head_decay = torch.tensor(self.decay_values, dtype=torch.float32, device=rt.device)     # a constant of the design, not a weight
+        self.w_in = self.w_o = self.norm_w = None
+
+    def cache_need(self):
+        return CompositeNeed((("state", FixedStateNeed((self.nh, self.dk, self.dv), torch.float32)),))
+
+    def _pieces(self):
+        n = self.names
+        return [(n["q"], 0), (n["k"], self.k_col), (n["v"], self.v_col), (n["gate"], self.g_col)]
+
+    def weight_specs(self) -> Dict[str, WeightSpec]:
+        n, W = self.names, self.hidden
+        return {n["q"]: WeightSpec((self.qk_cols, W)), n["k"]: WeightSpec((self.qk_cols, W)), n["v"]: WeightSpec((self.v_cols, W)),
+                n["gate"]: WeightSpec((self.v_cols, W)), n["norm"]: WeightSpec((self.v_cols,), role="vector", init=("one_plus_normal", 0.1)),
+                n["o"]: WeightSpec((W, self.v_cols))}
+
+    def fused_tensors(self):
+        return {"in_proj.weight": (WeightSpec((self.in_rows, self.hidden)), self._pieces())}
+
+    def kernel_sources(self):
+        own = linear_attention.sources()
+        return own if self.rt.is_fp32 else own + gemm_bf16.sources(engine_only=True)
+
+    def bind(self, tensors):
+        n = self.names
+        self.w_in = tensors["in_proj.weight"] if "in_proj.weight" in tensors else torch.cat([tensors[name] for name, _ in self._pieces()], 0).contiguous()
+        self.norm_w, self.w_o = tensors[n["norm"]], tensors[n["o"]]
+
+    def replay_key(self):
+        if not self.rt.is_fp32 and not gemm_bf16._direct_library(self.rt.device):
+            return None
+        return ("lightning_attention", self.hidden, self.nh, self.dk, self.dv, self.decay_values, self.eps)
+
+    def own_tensors(self):
+        return [self.w_in, self.w_o, self.norm_w]
+
+    def forward(self, x: torch.Tensor, ctx: StepContext, cache) -> torch.Tensor:
+        T, flag, f32 = x.shape[0], ctx.error_flag, torch.float32
+        state = cache["state"]
+        buf = lambda role, shape, dtype=f32: ctx.buffer("lightning." + role, shape, dtype)
+        proj = linear(x, self.w_in, None, f32, partials_ok=True, error_flag=flag, alloc=lambda shape, dtype: buf("proj", shape, dtype))
+        q, k, decay = buf("q", (T, self.qk_cols)), buf("k", (T, self.qk_cols)), buf("decay", (T, self.qk_cols))
+        v = buf("v", (T, self.v_cols))
+        linear_attention.lightning_prepare(proj, 0, self.k_col, self.v_col, self.head_decay, q, k, v, decay, self.nh, self.dk, self.dv)
+        o = buf("o", (T, self.v_cols))
+        recurrent.linear_scan("decayed_sum", q, k, decay, v, o, state.storage, state.slots, ctx, self.nh, self.dk, self.dv)
+        gated = buf("gated", (T, self.v_cols), self.rt.dtype)
+        linear_attention.row_norm_gate(o, self.norm_w, proj, self.g_col, gated, self.eps)
         return linear(gated, self.w_o, None, f32, partials_ok=True, error_flag=flag, alloc=lambda shape, dtype: buf("out", shape, dtype))
 
 

@@ -1,6 +1,7 @@
 """Gated feed-forward: down( act(gate(x)) * up(x) ), no biases; act = silu (SwiGLU, the default;
 reference: src/model/model.cpp:757-794; activation src/ops/ops.cpp:760-785) or the tanh form of gelu
-(`activation="gelu_tanh"`).  Gate and up are one fused product (gate rows first, then up rows)."""
+(`activation="gelu_tanh"`).  Gate and up are one fused product (gate rows first, then up rows).
+`activation="clamped_swish"` with `limit` L: g = min(gate(x), L), u = clamp(up(x), -L, L), down(g * sigmoid(1.702 g) * (u + 1))."""
 from __future__ import annotations
 
 from typing import Dict
@@ -12,6 +13,10 @@ from ..kernels.linear import linear
 from .base import FeedForward, Runtime, StepContext, WeightSpec, register_feed_forward, scratch
 
 
+CLAMPED = "clamped_swish"
+SWISH_ALPHA = 1.702
+
+
 @register_feed_forward("swiglu")
 class SwiGLU(FeedForward):
     def __init__(self, params: dict, rt: Runtime):
@@ -21,8 +26,12 @@ class SwiGLU(FeedForward):
         # local names of the three matrices in the checkpoint (gate, up, down)
         self.n_gate, self.n_up, self.n_down = params.get("names", ("gate_proj.weight", "up_proj.weight", "down_proj.weight"))
         self.activation = params.get("activation", "silu")
-        if self.activation not in ops.ACTIVATIONS:
-            raise ValueError(f"feed-forward activation {self.activation!r} is not one of {', '.join(ops.ACTIVATIONS)}")
+        self.limit = float(params["limit"]) if params.get("limit") is not None else None
+        if self.activation == CLAMPED:
+            if self.limit is None or not self.limit > 0:
+                raise ValueError("feed-forward activation 'clamped_swish' needs a positive limit")
+        elif self.activation not in ops.ACTIVATIONS:
+            raise ValueError(f"feed-forward activation {self.activation!r} is not one of {', '.join(ops.ACTIVATIONS)}, {CLAMPED}")
         self.rt = rt
         self.w_gate_up = self.w_down = None
 
@@ -32,7 +41,8 @@ class SwiGLU(FeedForward):
                 self.n_down: WeightSpec((self.hidden, self.inter))}
 
     def kernel_sources(self):
-        return [] if self.rt.is_fp32 else gemm_bf16.sources(engine_only=True)
+        own = [("residual.cu", {})] if self.activation == CLAMPED else []
+        return own if self.rt.is_fp32 else own + gemm_bf16.sources(engine_only=True)
 
     def fused_tensors(self):
         return {"gate_up_proj.weight": (WeightSpec((2 * self.inter, self.hidden)),
@@ -48,7 +58,7 @@ class SwiGLU(FeedForward):
     def replay_key(self):
         if not self.rt.is_fp32 and not gemm_bf16._direct_library(self.rt.device):
             return None                  # the library product would go through the tensor framework
-        return ("swiglu", self.hidden, self.inter, self.activation)
+        return ("swiglu", self.hidden, self.inter, self.activation, self.limit)
 
     def own_tensors(self):
         return [self.w_gate_up, self.w_down]
@@ -59,7 +69,13 @@ class SwiGLU(FeedForward):
         # boundary -- the reference's policy for its bf16 feed-forward (src/ops/optimized.cpp:676-683).
         act = scratch(ctx, "swiglu.act", (x.shape[0], self.inter), self.rt.dtype, x.device)
         flag = ctx.error_flag if ctx is not None else None      # one flag covers the step: whoever reads it sees every kernel's
-        if (x.dtype == torch.bfloat16 and x.shape[0] <= gemm_bf16.GEMV_SILU_MAX_TOKENS and gemm_bf16.gemv_preferred(x, self.w_gate_up)
+        if self.activation == CLAMPED:
+            # the products' epilogues know silu and gelu; this activation follows the product in a kernel of its own,
+            # from fp32 sums (split over K for a few tokens)
+            gate_up = linear(x, self.w_gate_up, None, torch.float32, partials_ok=True, error_flag=flag,
+                             alloc=lambda shape, dtype: scratch(ctx, "swiglu.gate_up_f32", shape, dtype, x.device))
+            ops.clamped_gate_mul(gate_up, act, self.limit, SWISH_ALPHA)
+        elif (x.dtype == torch.bfloat16 and x.shape[0] <= gemm_bf16.GEMV_SILU_MAX_TOKENS and gemm_bf16.gemv_preferred(x, self.w_gate_up)
                 and gemm_bf16.gemv_fused_supported(x, self.w_gate_up)):
             # a few tokens: one weight-streaming kernel, the activation is its epilogue
             gemm_bf16.gemv_silu_mul(x, self.w_gate_up, act, activation=self.activation)

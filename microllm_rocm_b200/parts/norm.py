@@ -1,4 +1,4 @@
-"""RMSNorm: y = x * (1 / sqrt(mean(x^2) + eps)) * w, all in fp32
+"""RMSNorm: y = x * (1 / sqrt(mean(x^2) + eps)) * w, all in fp32 (`one_plus`: the checkpoint stores w - 1, a weight around zero)
 (reference: src/ops/ops.cpp:684-699; fused with the residual add at :702-740).
 LayerNorm: y = (x - mean) / sqrt(mean((x - mean)^2) + eps) * w + b, all in fp32; besides the plain form it offers the
 step of a block that normalises AFTER its sums: x <- norm(alpha * x + weighted results), in place."""
@@ -20,16 +20,19 @@ class RMSNorm(Norm):
         self.eps = float(params["eps"])
         self.name = params.get("name", "weight")         # the weight's local name in the checkpoint
         self.absent = bool(params.get("absent", False))  # a norm in front of a sub-layer that the layer leaves out: no weight, never run
+        self.one_plus = bool(params.get("one_plus", False))   # the stored tensor is the weight minus one: 1 is added once, at bind, in fp32
         self.rt = rt
         self.weight: Optional[torch.Tensor] = None
 
     def weight_specs(self) -> Dict[str, WeightSpec]:
         if self.absent:
             return {}
-        return {self.name: WeightSpec((self.size,), role="vector", init=("one_plus_normal", 0.1))}
+        return {self.name: WeightSpec((self.size,), role="vector", init=("normal", 0.1) if self.one_plus else ("one_plus_normal", 0.1))}
 
     def bind(self, tensors):
         self.weight = tensors.get(self.name) if self.absent else tensors[self.name]
+        if self.one_plus and self.weight is not None:
+            self.weight = (self.weight.to(torch.float32) + 1.0).contiguous()
 
     def replay_key(self):
         return ("rmsnorm", self.size, self.eps)
