@@ -210,7 +210,7 @@ def parallel_layer(heads, kv_heads, dim, vdim, r_heads, r_dim, r_vdim, mlp, scal
 
 def _preset(vocab, width, layers, buckets):
     return {"architecture": ARCHITECTURE, "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "layers": layers,
-            "embedding": {"bigram": {"buckets": buckets, "mul_prev": 36313, "mul_cur": 27191}}, "logit_softcap": 30.0}
+            "embedding": {"bigram": {"buckets": buckets, "mul_prev": 36313, "mul_cur": 27191}}, "logit_softcap": 25.0}
 
 
 PRESETS: Dict[str, Dict[str, Any]] = {
