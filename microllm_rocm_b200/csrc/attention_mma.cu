@@ -62,11 +62,13 @@ struct FaParams {
     int num_heads, num_kv_heads, group;
     int chunk;               // > 0: only keys of the query's own block of `chunk` positions (counted from 0)
     int window;
-    float scale_log2;               // softmax scale * log2(e)
+    float scale_log2;               // softmax scale * log2(e); with a cap on the scores: cap * log2(e)
     int page_shift;                 // log2(page_size) when it is a power of two, else -1
     int* error_flag;
     int listed;                     // decode shape: 1 = work item i is sequence work[i] (a step that also holds prompt
                                     // portions), 0 = work item i is sequence i and token i (every sequence brings one token)
+    float cap_pre;                  // > 0: scores are capped, s <- cap * tanh(s * scale / cap); this is scale / cap
+    const float* sink;              // [num_heads] or null: exp(sink[head]) joins the head's denominator (no key, no value)
 };
 
 __device__ __forceinline__ void mma_bf16(float (&c)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3,
@@ -87,6 +89,27 @@ __device__ __forceinline__ float fast_exp2(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
+}
+
+// tanh by one exponential and one reciprocal: 1 - 2 / (2^(2x log2 e) + 1); absolute error of a few 1e-7, exact at both ends
+__device__ __forceinline__ float fast_tanh(float x) {
+    float r;
+    const float e = fast_exp2(x * (2.0f * LOG2E));
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(e + 1.0f));
+    return fmaf(-2.0f, r, 1.0f);
+}
+// a raw dot product -> the score in base-2 units: s * scale * log2(e), or with a cap: cap * tanh(s * scale / cap) * log2(e)
+__device__ __forceinline__ float score_log2(const FaParams& p, float s) {
+    return (p.cap_pre > 0.0f ? fast_tanh(s * p.cap_pre) : s) * p.scale_log2;
+}
+// What the accumulator of a row is multiplied by at the end: 1 / l, or with a sink 1 / (l + 2^(sink log2 e - m)), where the
+// row's sum l and its accumulator are relative to 2^m (m in base-2 units; -inf: the row saw no key).
+__device__ __forceinline__ float final_factor(const FaParams& p, int head, float m, float l) {
+    if (!p.sink) return l > 0.0f ? 1.0f / l : 0.0f;
+    if (m == -INFINITY) return 0.0f;
+    const float e = p.sink[head] * LOG2E - m, t = fmaxf(e, 0.0f);
+    const float shrink = exp2f(-t);
+    return shrink / (l * shrink + exp2f(e - t));
 }
 
 __device__ __forceinline__ uint4 load16(const __nv_bfloat16* p) {
@@ -222,7 +245,7 @@ __device__ __forceinline__ void consume_keys(const FaParams& p, const __nv_bfloa
                 const int i = e >> 1;
                 const int key = kv.base + nb * 8 + 2 * t + (e & 1);
                 const bool ok = key >= lo_row[i] && key <= pos_row[i];
-                s[nb][e] = ok ? s[nb][e] * p.scale_log2 : -INFINITY;
+                s[nb][e] = ok ? score_log2(p, s[nb][e]) : -INFINITY;
                 mx[i] = fmaxf(mx[i], s[nb][e]);
             }
     } else {
@@ -230,7 +253,7 @@ __device__ __forceinline__ void consume_keys(const FaParams& p, const __nv_bfloa
         for (int nb = 0; nb < 2; ++nb)
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
-                s[nb][e] *= p.scale_log2;
+                s[nb][e] = score_log2(p, s[nb][e]);
                 mx[e >> 1] = fmaxf(mx[e >> 1], s[nb][e]);
             }
     }
@@ -553,7 +576,7 @@ __global__ void __launch_bounds__(WARPS * 32, 2) fa_prefill_kernel(FaParams p) {
                 for (int nb = 0; nb < 8; ++nb)
 #pragma unroll
                     for (int e = 0; e < 4; ++e) {
-                        s[nb][e] *= p.scale_log2;
+                        s[nb][e] = score_log2(p, s[nb][e]);
                         mx[e >> 1] = fmaxf(mx[e >> 1], s[nb][e]);
                     }
             } else {
@@ -564,7 +587,7 @@ __global__ void __launch_bounds__(WARPS * 32, 2) fa_prefill_kernel(FaParams p) {
                         const int i = e >> 1;
                         const int key = base + nb * 8 + 2 * t + (e & 1);
                         const bool ok = key >= lo_row[i] && key <= pos_row[i];
-                        s[nb][e] = ok ? s[nb][e] * p.scale_log2 : -INFINITY;
+                        s[nb][e] = ok ? score_log2(p, s[nb][e]) : -INFINITY;
                         mx[i] = fmaxf(mx[i], s[nb][e]);
                     }
             }
@@ -621,7 +644,7 @@ __global__ void __launch_bounds__(WARPS * 32, 2) fa_prefill_kernel(FaParams p) {
         float l = l_run[i];
         l += __shfl_xor_sync(0xffffffffu, l, 1);
         l += __shfl_xor_sync(0xffffffffu, l, 2);
-        inv[i] = l > 0.0f ? 1.0f / l : 0.0f;
+        inv[i] = final_factor(p, geo.kvh * p.group + (geo.row0 + g + 8 * i) % p.group, m_run[i], l);
     }
     __syncwarp();
 #pragma unroll
@@ -805,7 +828,7 @@ __global__ void __launch_bounds__(DW * 32, DW == 4 ? 2 : 1) fa_decode_kernel(FaP
             }
         }
         const int head = geo.kvh * p.group + geo.row0 + r;
-        p.out[((size_t)geo.token0 * p.num_heads + head) * D + dim] = __float2bfloat16_rn(l_all > 0.0f ? acc / l_all : 0.0f);
+        p.out[((size_t)geo.token0 * p.num_heads + head) * D + dim] = __float2bfloat16_rn(acc * final_factor(p, head, m_all, l_all));
     }
     cluster.sync();                          // nobody leaves while its shared memory may still be read
 }
@@ -853,7 +876,7 @@ __device__ __forceinline__ void consume_keys_t(const FaParams& p, const __nv_bfl
     // s[0], s[1]: key base + g, heads 2t, 2t+1;   s[2], s[3]: key base + g + 8
     float s[4];
 #pragma unroll
-    for (int e = 0; e < 4; ++e) s[e] = (s0[e] + s1[e]) * p.scale_log2;
+    for (int e = 0; e < 4; ++e) s[e] = score_log2(p, s0[e] + s1[e]);
     if (kv.base + 15 > last_pos || kv.base < lo) {         // an edge tile (uniform over the warp)
         const int key0 = kv.base + g, key1 = key0 + 8;
         if (key0 < lo || key0 > last_pos) s[0] = s[1] = -INFINITY;
@@ -999,7 +1022,7 @@ __device__ __forceinline__ void merge_and_store_t(const FaParams& p, const TileG
             }
         }
         const int head = geo.kvh * p.group + r;
-        p.out[((size_t)geo.token0 * p.num_heads + head) * D + dim] = __float2bfloat16_rn(l_all > 0.0f ? acc / l_all : 0.0f);
+        p.out[((size_t)geo.token0 * p.num_heads + head) * D + dim] = __float2bfloat16_rn(acc * final_factor(p, head, m_all, l_all));
     }
     cluster.sync();                          // nobody leaves while its shared memory may still be read
 }
@@ -1386,8 +1409,8 @@ MLB_EXPORT int mlb_fa_max_splits() { return MAX_SPLITS; }
 MLB_EXPORT int mlb_paged_attention_mma(const void* q, const void* pages, void* out, const int* seq_starts,
                                        const int* seq_pos0, const int* block_table, const int* work, int num_work,
                                        int max_blocks, int num_pages, int page_size, int num_heads, int num_kv_heads,
-                                       int window, int chunk, float scale, int mode, int splits, int* error_flag,
-                                       cudaStream_t stream) {
+                                       int window, int chunk, float scale, int mode, int splits, const float* sink, float softcap,
+                                       int* error_flag, cudaStream_t stream) {
     if (num_heads <= 0 || num_kv_heads <= 0 || num_heads % num_kv_heads != 0)
         return fail(MLB_INVALID_ARGUMENT, "paged_attention_mma: bad head counts %d/%d", num_heads, num_kv_heads);
     if (page_size <= 0 || page_size % 16 != 0)
@@ -1405,8 +1428,9 @@ MLB_EXPORT int mlb_paged_attention_mma(const void* q, const void* pages, void* o
     if (num_work == 0) return MLB_OK;
     FaParams p{(const __nv_bfloat16*)q, (const __nv_bfloat16*)pages, (__nv_bfloat16*)out, seq_starts, seq_pos0,
                block_table, work, max_blocks, num_pages, page_size, num_heads, num_kv_heads,
-               num_heads / num_kv_heads, chunk, window, scale * LOG2E, (page_size & (page_size - 1)) == 0 ? __builtin_ctz((unsigned)page_size) : -1, error_flag,
-               mode == 2 ? 1 : 0};
+               num_heads / num_kv_heads, chunk, window, softcap > 0.0f ? softcap * LOG2E : scale * LOG2E,
+               (page_size & (page_size - 1)) == 0 ? __builtin_ctz((unsigned)page_size) : -1, error_flag,
+               mode == 2 ? 1 : 0, softcap > 0.0f ? scale / softcap : 0.0f, sink};
     if (mode == 0) {
         static bool prefill_configured_on[MAX_DEVICES] = {false};
         bool& prefill_configured = prefill_configured_on[device_index()];

@@ -75,8 +75,10 @@ struct TcParams {
     const int* work;                // [num_work, 2] (sequence, 128-row tile of its new tokens)
     int max_blocks, num_pages, page_size, pages_per_tile;
     int num_heads, num_kv_heads, group, window, chunk;
-    float scale_log2;
+    float scale_log2;               // softmax scale * log2(e); with a cap on the scores: cap * log2(e)
     int* error_flag;
+    float cap_pre;                  // > 0: scores are capped, s <- cap * tanh(s * scale / cap); this is scale / cap
+    const float* sink;              // [num_heads] or null: exp(sink[head]) joins the head's denominator (no key, no value)
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -391,6 +393,16 @@ fa_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(&s_empty[buf]));
 
+            if (p.cap_pre > 0.0f) {
+                // tanh by one exponential and one reciprocal: 1 - 2 / (2^(2x log2 e) + 1)
+#pragma unroll
+                for (int c = 0; c < BN; ++c) {
+                    float rcp;
+                    const float e = fast_exp2(__uint_as_float(sr[c]) * (p.cap_pre * 2.0f * LOG2E));
+                    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(rcp) : "f"(e + 1.0f));
+                    sr[c] = __float_as_uint(fmaf(-2.0f, rcp, 1.0f));
+                }
+            }
             const int kbase = (kt_begin + j) * BN;
             const bool edge = (kbase + BN - 1 > qpos_first) || (kbase < first_visible_key(qpos_last, p.window, p.chunk));
             float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};       // four chains: no 128-long dependence
@@ -472,7 +484,13 @@ fa_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
         if (ok && n_tiles > 0) ok = wait_all(&pv_done[(n_tiles - 1) & 1], ((n_tiles - 1) >> 1) & 1, 31);
         if (ok && n_tiles > 0) {
             tc_fence_after();
-            const float inv = l > 0.0f ? 1.0f / l : 0.0f;
+            float inv = l > 0.0f ? 1.0f / l : 0.0f;
+            if (p.sink) {
+                // the sink joins last: l and the accumulator are relative to 2^m_used
+                const float e = p.sink[head] * LOG2E - (m_used == -INFINITY ? 0.0f : m_used), t = fmaxf(e, 0.0f);
+                const float shrink = exp2f(-t);
+                inv = m_used == -INFINITY ? 0.0f : shrink / (l * shrink + exp2f(e - t));
+            }
             __nv_bfloat16* orow = p.out + (size_t)(token0 + row_first + r) * p.ldo + (size_t)head * D;
 #pragma unroll
             for (int c = 0; c < D / 32; ++c) {
@@ -558,7 +576,8 @@ MLB_EXPORT int mlb_fa_tc_supported(int page_size, float scale) {
 MLB_EXPORT int mlb_paged_attention_tc(const void* q, long long ldq, const void* pages, void* out, long long ldo, int tokens,
                                       const int* seq_starts, const int* seq_pos0, const int* block_table, const int* work,
                                       int num_work, int max_blocks, int num_pages, int page_size, int num_heads,
-                                      int num_kv_heads, int window, int chunk, float scale, int* error_flag, cudaStream_t stream) {
+                                      int num_kv_heads, int window, int chunk, float scale, const float* sink, float softcap,
+                                      int* error_flag, cudaStream_t stream) {
     if (num_heads <= 0 || num_kv_heads <= 0 || num_heads % num_kv_heads != 0)
         return fail(MLB_INVALID_ARGUMENT, "attention_tc: bad head counts %d/%d", num_heads, num_kv_heads);
     if (!mlb_fa_tc_supported(page_size, scale)) return MLB_UNSUPPORTED_SIZE;
@@ -579,7 +598,8 @@ MLB_EXPORT int mlb_paged_attention_tc(const void* q, long long ldq, const void* 
     if (status != MLB_OK) return status;
 
     TcParams p{(__nv_bfloat16*)out, ldo, seq_starts, seq_pos0, block_table, work, max_blocks, num_pages, page_size,
-               BN / page_size, num_heads, num_kv_heads, num_heads / num_kv_heads, window, chunk, scale * LOG2E, error_flag};
+               BN / page_size, num_heads, num_kv_heads, num_heads / num_kv_heads, window, chunk,
+               softcap > 0.0f ? softcap * LOG2E : scale * LOG2E, error_flag, softcap > 0.0f ? scale / softcap : 0.0f, sink};
     static bool configured_on[MAX_DEVICES] = {false};         // the attribute belongs to the device
     bool& configured = configured_on[device_index()];
     if (!configured) {

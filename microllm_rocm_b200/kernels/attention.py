@@ -49,11 +49,11 @@ TC_MIN_NEW_TOKENS = 2
 ops.register_signatures("attention_tc.cu", {
     "mlb_fa_tc_supported": [c_int, c_float],
     "mlb_paged_attention_tc": [c_void_p, c_longlong, c_void_p, c_void_p, c_longlong, c_int, c_void_p, c_void_p, c_void_p,
-                               c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p],
+                               c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_float, c_void_p, c_void_p],
 })
 ops.register_signatures("attention_mma.cu", {
     "mlb_paged_attention_mma": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
-                                c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_void_p],
+                                c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_float, c_void_p, c_void_p],
 })
 
 
@@ -72,8 +72,9 @@ def mma_sources(head_dim: int):
 
 
 def extras_supported(head_dim: int, softcap, sink: bool) -> bool:
-    """Whether the tensor-core kernels of one width take a cap on the scores and a sink in the denominator."""
-    return not softcap and not sink
+    """Whether the tensor-core kernels of one width take a cap on the scores and a sink in the denominator: both, at every
+    head size (the cap bends the score before the running maximum sees it; the sink joins the row's sum at the very end)."""
+    return True
 
 
 def tc_supported(head_dim: int, page_size: int, scale: float) -> bool:
@@ -181,12 +182,22 @@ def _plan(ctx, group: int, num_kv_heads: int, use_tc: bool, beside_mma_products:
 
 def paged_attention(q: torch.Tensor, pages: torch.Tensor, out: torch.Tensor, ctx, block_table: torch.Tensor,
                     num_heads: int, num_kv_heads: int, head_dim: int, scale: float, window: Optional[int],
-                    beside_mma_products: bool = False, chunk: Optional[int] = None) -> None:
+                    beside_mma_products: bool = False, chunk: Optional[int] = None, sink: Optional[torch.Tensor] = None,
+                    softcap: float = 0.0) -> None:
     """`chunk`: a query sees only the keys of its own block of `chunk` positions (blocks counted from position 0 of the
     sequence), on top of the causal rule and the window.  `beside_mma_products`: the projections around this attention run on the few-token mma.sync kernels in this
-    step (a choice of the caller's products; it decides which decode kernel suits, see decode_ring_pays)."""
+    step (a choice of the caller's products; it decides which decode kernel suits, see decode_ring_pays).
+    `softcap` > 0: scores become softcap * tanh(score / softcap).  `sink` [heads] fp32: exp(sink) joins each head's denominator
+    (with no key and no value, neither scaled nor capped).  Both only on the tensor-core kernels."""
     page_size = pages.shape[3]
+    softcap = float(softcap or 0.0)
+    if sink is not None:
+        ops._need(sink, "sink", torch.float32, 1)
+        if sink.shape[0] != num_heads:
+            raise KernelError("paged_attention: one sink per head")
     if q.dtype != torch.bfloat16 or not mma_supported(head_dim, page_size):
+        if sink is not None or softcap:
+            raise KernelError("paged_attention: the plain kernel of one width has neither sink nor cap (use attention_kv.paged_attention_kv)")
         ops.paged_attention_plain(q, pages, out, ctx.positions, ctx.token_seq, block_table, num_heads, num_kv_heads,
                                   head_dim, scale, window, ctx.error_flag, chunk=chunk)
         return
@@ -210,8 +221,8 @@ def paged_attention(q: torch.Tensor, pages: torch.Tensor, out: torch.Tensor, ctx
         build.check(T, T.mlb_paged_attention_tc(
             q.data_ptr(), q.stride(0), pages.data_ptr(), out.data_ptr(), out.stride(0), q.shape[0], ctx.seq_starts.data_ptr(),
             ctx.seq_pos0.data_ptr(), block_table.data_ptr(), tc_work.data_ptr(), num_tc, block_table.shape[1],
-            pages.shape[0], page_size, num_heads, num_kv_heads, int(window or 0), int(chunk or 0), float(scale), ops._ptr(ctx.error_flag),
-            stream))
+            pages.shape[0], page_size, num_heads, num_kv_heads, int(window or 0), int(chunk or 0), float(scale), ops._ptr(sink), softcap,
+            ops._ptr(ctx.error_flag), stream))
     if not num_work and not num_listed:
         return
     L = ops.lib("attention_mma.cu", {"HEAD_DIM": head_dim})
@@ -220,11 +231,12 @@ def paged_attention(q: torch.Tensor, pages: torch.Tensor, out: torch.Tensor, ctx
         build.check(L, L.mlb_paged_attention_mma(
             q.data_ptr(), pages.data_ptr(), out.data_ptr(), ctx.seq_starts.data_ptr(), ctx.seq_pos0.data_ptr(), block_table.data_ptr(),
             listed.data_ptr(), num_listed, block_table.shape[1], pages.shape[0], page_size, num_heads, num_kv_heads,
-            int(window or 0), int(chunk or 0), float(scale), 2 + ring_bits, listed_splits, ops._ptr(ctx.error_flag), ops._stream()))
+            int(window or 0), int(chunk or 0), float(scale), 2 + ring_bits, listed_splits, ops._ptr(sink), softcap, ops._ptr(ctx.error_flag),
+            ops._stream()))
     if num_work:
         build.check(L, L.mlb_paged_attention_mma(
             q.data_ptr(), pages.data_ptr(), out.data_ptr(), ctx.seq_starts.data_ptr(), ctx.seq_pos0.data_ptr(), block_table.data_ptr(), work.data_ptr(), num_work,
             block_table.shape[1], pages.shape[0], page_size, num_heads, num_kv_heads, int(window or 0), int(chunk or 0), float(scale),
-            mode + (ring_bits if mode else 0), splits, ops._ptr(ctx.error_flag), ops._stream()))
+            mode + (ring_bits if mode else 0), splits, ops._ptr(sink), softcap, ops._ptr(ctx.error_flag), ops._stream()))
     if side is not None:
         ops.join(side)

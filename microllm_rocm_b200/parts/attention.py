@@ -414,13 +414,22 @@ class NormedAttention(Mixer):
         if self._shared_kernels(kv_view.page_size):
             wide = o if (sv == self.dv and gate is None) else ctx.buffer("normed_attention.o_stored", (T, self.nh * sv), dt)
             attention_kernels.paged_attention(q, kv_view.pages, wide, ctx, kv_view.block_table, self.nh, self.nkv, sk, self.scale,
-                                              self.window, beside_mma_products=gemm_bf16.gemv_preferred(x, self.w_o), chunk=self.chunk)
+                                              self.window, beside_mma_products=gemm_bf16.gemv_preferred(x, self.w_o), chunk=self.chunk,
+                                              sink=self.sink, softcap=self.softcap or 0.0)
             if wide is not o:
                 attention_kv.gate_heads(wide, o, gate, self.conv_cols, self.nh, self.dv, sv, per_head=self.gate_per_head)
-        elif self.stored is not None:            # a page size the tensor-core kernels do not take: the plain kernel of one width
+        elif self.stored is not None and self.sink is None and not self.softcap:
+            # a page size the tensor-core kernels do not take: the plain kernel of one width
             wide = ctx.buffer("normed_attention.o_stored", (T, self.nh * sv), dt)
             attention_kernels.paged_attention(q, kv_view.pages, wide, ctx, kv_view.block_table, self.nh, self.nkv, sk, self.scale, self.window,
                                               chunk=self.chunk)
+            attention_kv.gate_heads(wide, o, gate, self.conv_cols, self.nh, self.dv, sv, per_head=self.gate_per_head)
+        elif self.stored is not None:
+            # the same with a sink or a cap: the plain kernel of two widths, told that both are the stored one
+            wide = ctx.buffer("normed_attention.o_stored", (T, self.nh * sv), dt)
+            attention_kv.paged_attention_kv(q, kv_view.pages, wide, ctx.positions, ctx.token_seq, kv_view.block_table, kv_view.page_size,
+                                            self.nh, self.nkv, sk, sv, self.scale, self.window, None, 0, flag, chunk=self.chunk,
+                                            sink=self.sink, softcap=self.softcap or 0.0)
             attention_kv.gate_heads(wide, o, gate, self.conv_cols, self.nh, self.dv, sv, per_head=self.gate_per_head)
         else:
             attention_kv.paged_attention_kv(q, kv_view.pages, o, ctx.positions, ctx.token_seq, kv_view.block_table, kv_view.page_size,

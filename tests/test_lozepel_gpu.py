@@ -360,6 +360,69 @@ def test_cap_on_the_logits():
     assert torch.allclose(x.double(), want, atol=1e-5)
 
 
+def one_width_step(pages, table, lens, q_list, news, nh, nkv, d, scale, sink, cap):
+    """One step on the attention kernels of one width: sequence s brings news[s] queries at its last positions."""
+    from microllm_rocm_b200.kernels import attention
+    from microllm_rocm_b200.parts.base import StepContext
+    pos0 = [l - n for l, n in zip(lens, news)]
+    starts = [0]
+    for n in news:
+        starts.append(starts[-1] + n)
+    q = torch.cat([x.reshape(x.shape[0], nh * d) for x in q_list]).contiguous()
+    positions = torch.cat([torch.arange(p, p + n, dtype=torch.int32) for p, n in zip(pos0, news)]).to(DEV)
+    token_seq = torch.cat([torch.full((n,), s, dtype=torch.int32) for s, n in enumerate(news)]).to(DEV)
+    flag = torch.zeros(1, dtype=torch.int32, device=DEV)
+    out = torch.full(q.shape, float("nan"), dtype=torch.bfloat16, device=DEV)
+    ctx = StepContext(num_tokens=q.shape[0], num_seqs=len(news), token_ids=positions, positions=positions, token_seq=token_seq,
+                      seq_starts=i32(starts), seq_pos0=i32(pos0), seq_lens=i32(lens), block_tables={}, state_slots=None,
+                      logit_rows=None, error_flag=flag, seq_starts_host=starts, seq_pos0_host=pos0,
+                      max_new_tokens=max(news), max_seq_len=max(lens))
+    attention.paged_attention(q, pages, out, ctx, table, nh, nkv, d, scale, None, sink=sink, softcap=cap or 0.0)
+    torch.cuda.synchronize()
+    assert int(flag.item()) == 0
+    return out.float().reshape(-1, nh, d)
+
+
+@pytest.mark.parametrize("d, page", [(64, 16), (128, 64), (32, 16), (256, 16)])
+@pytest.mark.parametrize("sink, cap", [((2.0, -1.0, 0.0, 5.0), None), ((0.5, 0.5, 3.0, -2.0), 1.5), (None, 4.0), ((60.0, -60.0, 9.0, 0.0), None)])
+def test_sink_and_cap_on_the_kernels_of_one_width(d, page, sink, cap):
+    """bf16, the tensor-core kernels (prompt portions, every decode form, decoded tokens beside portions) against the formula
+    over the same bf16 keys and values: sinks of both signs (one far above every score, one far below), a tight cap."""
+    from microllm_rocm_b200.kernels import attention
+    if not attention.mma_supported(d, page):
+        pytest.skip("no tensor-core kernel for this head size and page size")
+    nh, nkv, n = 4, 2, 700
+    gen = torch.Generator(device=DEV).manual_seed(d + (7 if cap else 0))
+    blocks = -(-n // page)
+    pages = torch.randn((blocks + 2, 2, nkv, page, d), generator=gen, device=DEV).bfloat16()
+    table = torch.randperm(blocks + 2, generator=gen, device=DEV).to(torch.int32)[:blocks].view(1, blocks).contiguous()
+    got = pages[table[0].long()]
+    k = got[:, 0].permute(0, 2, 1, 3).reshape(-1, nkv, d)[:n].double().cpu()
+    v = got[:, 1].permute(0, 2, 1, 3).reshape(-1, nkv, d)[:n].double().cpu()
+    q = (torch.randn((n, nh, d), generator=gen, device=DEV) * 2.0).bfloat16()
+    scale = 2.0 / math.sqrt(d)
+    sink_t = torch.tensor(sink, dtype=torch.float32, device=DEV) if sink else None
+    want = plain.sink_attention(q.double().cpu(), k, v, scale, torch.tensor(sink if sink else [-1e30] * nh, dtype=F64), cap)
+
+    def check(out, rows, what):
+        ref = want[rows]
+        err = (out.double().cpu() - ref).abs().amax(-1) / ref.abs().amax(-1).clamp_min(0.05)
+        assert torch.isfinite(out).all() and float(err.max()) < 0.04, (what, float(err.max()), int(err.argmax()))
+
+    check(one_width_step(pages, table, [n], [q], [n], nh, nkv, d, scale, sink_t, cap), slice(0, n), "whole prompt")
+    check(one_width_step(pages, table, [n], [q[300:]], [n - 300], nh, nkv, d, scale, sink_t, cap), slice(300, n), "portion")
+    for pos in (0, 1, 127, 128, n - 1):
+        check(one_width_step(pages, table, [pos + 1], [q[pos:pos + 1]], [1], nh, nkv, d, scale, sink_t, cap), slice(pos, pos + 1), f"decoded token at {pos}")
+    lens = [1, 130, 500, n]                                                      # several decoded tokens of unequal contexts in one step
+    outs = one_width_step(pages, table.expand(4, -1).contiguous(), lens, [q[l - 1:l] for l in lens], [1] * 4, nh, nkv, d, scale, sink_t, cap)
+    for i, l in enumerate(lens):
+        check(outs[i:i + 1], slice(l - 1, l), f"batched decode at {l - 1}")
+    # a portion of one sequence beside a decoded token of another (the same pages under two tables)
+    both = one_width_step(pages, table.expand(2, -1).contiguous(), [400, n], [q[250:400], q[n - 1:n]], [150, 1], nh, nkv, d, scale, sink_t, cap)
+    check(both[:150], slice(250, 400), "portion beside a decoded token")
+    check(both[150:], slice(n - 1, n), "decoded token beside a portion")
+
+
 # ------------------------------------------------------------------------------------------- whole models
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("key", sorted(CASES))
