@@ -311,6 +311,13 @@ def step_timeline(session):
 # expert) stand beside the closest design that was here before, a Matidra of the same width, layers and vocabulary: its
 # parallel layers take the heads and widths of Fonuvik's two sides, and its dense feed-forward is as wide as what a
 # Fonuvik token runs (its chosen experts plus the shared one).
+# The Lozepel sizes (a pair-table embedding; norms on both sides of every sublayer; a layer of attention whose values are the
+# keys, with biases, one added to the denominator and a gate per head; a layer of attention with whole-row norms and learned
+# sinks beside linear attention with one fixed decay per head; two layers of capped attention with sinks, the second reading
+# the first one's keys and values; a clamped dense feed-forward, then routed experts with outputs that pass the input on)
+# stand beside the closest design that was here before, a Fonuvik of the same width, layers and vocabulary: parallel layers
+# with the heads and widths of Lozepel's two sides where Lozepel has a softmax mixer, and routed experts of the same count
+# and width (plus a shared expert as wide as Lozepel's dense feed-forward where Lozepel has that).
 DESIGN_SIZES = {
     "small": dict(gedalix="gedalix-small", layers=4),
     "16b-layers": dict(gedalix="gedalix-16b-layers", layers=4),
@@ -318,6 +325,8 @@ DESIGN_SIZES = {
     "matidra-3b-layers": dict(matidra="matidra-3b-layers", layers=4),
     "fonuvik-small": dict(fonuvik="fonuvik-small", layers=4),
     "fonuvik-3b-layers": dict(fonuvik="fonuvik-3b-layers", layers=4),
+    "lozepel-small": dict(lozepel="lozepel-small", layers=4),
+    "lozepel-3b-layers": dict(lozepel="lozepel-3b-layers", layers=4),
 }
 
 
@@ -358,6 +367,23 @@ def _equal_matidra_fonuvik(raw, layers, max_positions):
                                     "postln_alpha": 2.0, "layers": made, "max_positions": max_positions})
 
 
+def _equal_fonuvik_lozepel(raw, layers, max_positions):
+    from microllm_rocm_b200.config.fonuvik import FonuvikConfig, moe, parallel_layer
+    par = next(l for l in raw["layers"] if l["type"] == "parallel")
+    right = par["mixer"]["right"]
+    routed = next(l["mlp"] for l in raw["layers"] if l.get("mlp") and l["mlp"]["kind"] == "moe")
+    made = []
+    for layer in raw["layers"][:layers]:
+        m = layer["mixer"]["left"] if layer["type"] == "parallel" else layer["mixer"]
+        mlp = layer.get("mlp")
+        shared = mlp["ff"] if mlp and mlp["kind"] == "dense" else None
+        made.append(parallel_layer(m["heads"], m["kv_heads"], m["dim"], m["vdim"], right["heads"], right["dim"], right["vdim"],
+                                   moe(routed["router"]["experts"], routed["router"]["top"], routed["expert"]["ff"], shared) if mlp else None,
+                                   block=max_positions, rot_dims=m["dim"], rank=64))
+    return FonuvikConfig.from_dict({"architecture": "Fonuvik", "vocab": raw["vocab"], "width": raw["width"], "norm": {"eps": 1e-6},
+                                    "layers": made, "max_positions": max_positions})
+
+
 def _kernel_rows(step_fn, repeats=3):
     """(name, launches, summed duration in us, summed exposed time in us: see _exposed) of one call of step_fn, the
     kernels that add most to the step first.  Kernels start early behind their predecessors, so a duration holds
@@ -393,7 +419,13 @@ def run_designs(args):
     for name in names:
         size = DESIGN_SIZES[name]
         layers = args.layers or size["layers"]
-        if "fonuvik" in size:
+        if "lozepel" in size:
+            from microllm_rocm_b200.config.lozepel import PRESETS as LOZEPEL_PRESETS, LozepelConfig
+            raw = copy.deepcopy(LOZEPEL_PRESETS[size["lozepel"]])
+            raw["layers"] = raw["layers"][:layers]
+            raw["max_positions"] = args.prompt + 512
+            designs = {"lozepel": LozepelConfig.from_dict(raw), "fonuvik": _equal_fonuvik_lozepel(raw, layers, args.prompt + 512)}
+        elif "fonuvik" in size:
             from microllm_rocm_b200.config.fonuvik import PRESETS as FONUVIK_PRESETS, FonuvikConfig
             raw = copy.deepcopy(FONUVIK_PRESETS[size["fonuvik"]])
             raw["layers"] = raw["layers"][:layers]

@@ -221,10 +221,10 @@ PRESETS: Dict[str, Dict[str, Any]] = {
     "lozepel-small": _preset(32000, 1024, [attention_layer(16, 4, 64, dense(2816), rot_dims=64),
                                            parallel_layer(16, 4, 64, 64, 8, 64, 128, moe(16, 2, 704, identity=2)),
                                            capped_layer(16, 4, 64, 64, moe(16, 2, 704, identity=2), rot_dims=64),
-                                           capped_layer(16, 4, 64, 64, moe(16, 2, 704, identity=2), rot_dims=64, kv_from=2)], buckets=65521),
+                                           capped_layer(16, 4, 64, 64, moe(16, 2, 704, identity=2), rot_dims=64, kv_from=2)], buckets=32749),
     "lozepel-3b-layers": _preset(102400, 2048, [attention_layer(16, 4, 128, dense(5632), rot_dims=128),
                                                 parallel_layer(16, 4, 128, 128, 16, 64, 128, moe(32, 4, 704, identity=2)),
                                                 capped_layer(16, 4, 128, 128, moe(32, 4, 704, identity=2), rot_dims=128),
                                                 capped_layer(16, 4, 128, 128, moe(32, 4, 704, identity=2), rot_dims=128, kv_from=2)],
-                                 buckets=262139),
+                                 buckets=65521),
 }

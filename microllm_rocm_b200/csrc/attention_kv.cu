@@ -298,6 +298,34 @@ row_norm_columns_kernel(Columns src, int cols, int col_a, int n_a, const float* 
     }
 }
 
+
+// The same for bf16 rows whose widths are multiples of 8: a thread moves 8 elements of one head (16 bytes); with one gate per
+// head it reads that gate once.
+__global__ void gate_heads_x8_kernel(GateParams p) {
+    pdl_prologue();
+    const int per_head = p.DV / 8, per_token = p.H * per_head;
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (long long)p.T * per_token) return;
+    const long long t = i / per_token;
+    const int rest = (int)(i % per_token), h = rest / per_head, c = (rest % per_head) * 8;
+    uint4 raw = *reinterpret_cast<const uint4*>((const __nv_bfloat16*)p.o + (t * p.H + h) * p.PV + c);
+    if (p.gate.base) {
+        __nv_bfloat162* pair = reinterpret_cast<__nv_bfloat162*>(&raw);
+        const float head_gate = p.gate_per_head ? sigmoid_f32(p.gate.at(t, p.gate_col + h)) : 1.0f;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            float2 v = __bfloat1622float2(pair[k]);
+            if (p.gate_per_head) { v.x *= head_gate; v.y *= head_gate; }
+            else {
+                v.x *= sigmoid_f32(p.gate.at(t, p.gate_col + h * p.DV + c + 2 * k));
+                v.y *= sigmoid_f32(p.gate.at(t, p.gate_col + h * p.DV + c + 2 * k + 1));
+            }
+            pair[k] = __floats2bfloat162_rn(v.x, v.y);
+        }
+    }
+    *reinterpret_cast<uint4*>((__nv_bfloat16*)p.out + (t * p.H + h) * p.DV + c) = raw;
+}
+
 }  // namespace
 
 MLB_EXPORT int mlb_row_norm_columns(const float* src, long long ld, int n_partials, long long partial_stride, int T, int cols,
@@ -321,7 +349,9 @@ MLB_EXPORT int mlb_gate_heads(const void* o, void* out, int dtype, const float* 
                  gate_per_head ? 1 : 0};
     const long long n = (long long)T * H * DV;
     const unsigned blocks = (unsigned)((n + 255) / 256);
-    if (dtype == MLB_BF16) launch_kernel(gate_heads_kernel<__nv_bfloat16>, blocks, 256, 0, stream, p);
+    if (dtype == MLB_BF16 && DV % 8 == 0 && stored_v % 8 == 0 && ((uintptr_t)o | (uintptr_t)out) % 16 == 0)
+        launch_kernel(gate_heads_x8_kernel, (unsigned)((n / 8 + 255) / 256), 256, 0, stream, p);
+    else if (dtype == MLB_BF16) launch_kernel(gate_heads_kernel<__nv_bfloat16>, blocks, 256, 0, stream, p);
     else if (dtype == MLB_F32) launch_kernel(gate_heads_kernel<float>, blocks, 256, 0, stream, p);
     else return fail(MLB_INVALID_ARGUMENT, "gate_heads: unsupported dtype %d", dtype);
     return check_launch("gate_heads");

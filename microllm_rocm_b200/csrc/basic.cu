@@ -214,6 +214,18 @@ __device__ __forceinline__ float gate_activation(float g, int act) {
     return g * stable_sigmoid(g);
 }
 
+// The whole gated value.  act 0 and 1: act(gate) * up.  Any larger act is the bit pattern of a positive fp32 limit L and asks
+// for the clamped form: g = min(gate, L), u = clamp(up, -L, L), g * sigmoid(1.702 g) * (u + 1).
+__device__ __forceinline__ float gated_value(float g, float u, int act) {
+    if (act > 1) {
+        const float limit = __int_as_float(act);
+        g = fminf(g, limit);
+        u = fminf(fmaxf(u, -limit), limit);
+        return g * (1.0f / (1.0f + expf(-1.702f * g))) * (u + 1.0f);
+    }
+    return gate_activation(g, act) * u;
+}
+
 template <typename InT, typename OutT>
 __global__ void silu_mul_kernel(const InT* __restrict__ gate, const InT* __restrict__ up, long long in_stride,
                                 int n_partials, long long partial_stride, OutT* __restrict__ out, int rows, int width, int act) {
@@ -227,7 +239,7 @@ __global__ void silu_mul_kernel(const InT* __restrict__ gate, const InT* __restr
         g += to_f32(gate[(size_t)k * partial_stride + r * in_stride + c]);
         u += to_f32(up[(size_t)k * partial_stride + r * in_stride + c]);
     }
-    out[i] = from_f32<OutT>(gate_activation(g, act) * u);
+    out[i] = from_f32<OutT>(gated_value(g, u, act));
 }
 
 // bf16 in, bf16 out, eight elements per thread (16-byte loads and stores)
@@ -247,7 +259,7 @@ __global__ void silu_mul_bf16x8_kernel(const __nv_bfloat16* __restrict__ gate, c
 #pragma unroll
     for (int k = 0; k < 4; ++k) {
         const float2 g = __bfloat1622float2(g2[k]), u = __bfloat1622float2(u2[k]);
-        o2[k] = __floats2bfloat162_rn(gate_activation(g.x, act) * u.x, gate_activation(g.y, act) * u.y);
+        o2[k] = __floats2bfloat162_rn(gated_value(g.x, u.x, act), gated_value(g.y, u.y, act));
     }
     *reinterpret_cast<uint4*>(out + (size_t)r * width + c) = ov;
 }
@@ -258,7 +270,7 @@ __global__ void silu_mul_bf16x8_kernel(const __nv_bfloat16* __restrict__ gate, c
 static int gated_act_mul(const void* gate, const void* up, long long in_stride, int in_dtype, int n_partials,
                          long long partial_stride, void* out, int out_dtype, int rows, int width, int act,
                          cudaStream_t stream) {
-    if (act != 0 && act != 1) return fail(MLB_INVALID_ARGUMENT, "gated activation: unknown activation %d", act);
+    if (act < 0) return fail(MLB_INVALID_ARGUMENT, "gated activation: unknown activation %d", act);
     if (rows < 0 || width <= 0 || in_stride < width || n_partials < 1) return fail(MLB_INVALID_ARGUMENT, "silu_mul: bad sizes");
     if (rows == 0) return MLB_OK;
     const long long n = (long long)rows * width;

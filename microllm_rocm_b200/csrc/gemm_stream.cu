@@ -67,7 +67,7 @@ struct StreamParams {
     int stages;
     int mode;
     int up_offset;             // SILU: first up row of the fused weight
-    int act;                   // SILU: the gate's activation (0 silu, 1 gelu_tanh)
+    int act;                   // SILU: the gate's activation (0 silu, 1 gelu_tanh, else the bits of the clamped form's limit: gated_value)
     int tmem_cols;
 };
 
@@ -144,6 +144,18 @@ __device__ __forceinline__ float gate_activation(float g, int act) {
     if (act == 0) return silu(g);
     const float y = 0.7978845608028654f * (g + 0.044715f * g * g * g);
     return 0.5f * g * (2.0f - __fdividef(2.0f, 1.0f + __expf(2.0f * y)));
+}
+
+// The whole gated value.  act 0 and 1: act(gate) * up.  Any larger act is the bit pattern of a positive fp32 limit L and asks
+// for the clamped form: g = min(gate, L), u = clamp(up, -L, L), g * sigmoid(1.702 g) * (u + 1).
+__device__ __forceinline__ float gated_value(float g, float u, int act) {
+    if (act > 1) {
+        const float limit = __int_as_float(act);
+        g = fminf(g, limit);
+        u = fminf(fmaxf(u, -limit), limit);
+        return g * __fdividef(1.0f, 1.0f + __expf(-1.702f * g)) * (u + 1.0f);
+    }
+    return gate_activation(g, act) * u;
 }
 
 // Where the 128 rows of work item `tile` come from: two boxes of 64 weight rows.
@@ -345,10 +357,10 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
                     float res[8];
                     if (!up_side) {
 #pragma unroll
-                        for (int j = 0; j < 8; ++j) res[j] = gate_activation(__uint_as_float(raw[j]), p.act) * xb[j * HALF_W + i];
+                        for (int j = 0; j < 8; ++j) res[j] = gated_value(__uint_as_float(raw[j]), xb[j * HALF_W + i], p.act);
                     } else {
 #pragma unroll
-                        for (int j = 0; j < 8; ++j) res[j] = gate_activation(xb[(8 + j) * HALF_W + i], p.act) * __uint_as_float(raw[8 + j]);
+                        for (int j = 0; j < 8; ++j) res[j] = gated_value(xb[(8 + j) * HALF_W + i], __uint_as_float(raw[8 + j]), p.act);
                     }
                     __nv_bfloat16* dst = p.out + (size_t)(c + (up_side ? 8 : 0)) * p.ldo + f;
                     const int left = p.M - c - (up_side ? 8 : 0);
@@ -535,7 +547,7 @@ MLB_EXPORT int mlb_gemm_stream_silu(const void* x, long long ldx, const void* w,
 MLB_EXPORT int mlb_gemm_stream_gated(const void* x, long long ldx, const void* w, long long ldw, int w_rows, int up_offset,
                                      void* out, long long ldo, int M, int I, int K, int stages, int act, int* error_flag,
                                      cudaStream_t stream) {
-    if (act != 0 && act != 1) return fail(MLB_INVALID_ARGUMENT, "gemm_stream_gated: unknown activation %d", act);
+    if (act < 0) return fail(MLB_INVALID_ARGUMENT, "gemm_stream_gated: unknown activation %d", act);
     int status = check_operands(x, ldx, w, ldw, M, K);
     if (status != MLB_OK) return status;
     if (I <= 0 || up_offset < I || up_offset + I > w_rows || ldo < I || !out)

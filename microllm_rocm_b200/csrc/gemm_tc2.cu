@@ -57,7 +57,7 @@ struct PairParams {
     int k_blocks, stages;
     int out_bf16;
     int accumulate;            // out += result (fp32 out only)
-    int dual;                  // 1: silu(gate) * up, 2: gelu_tanh(gate) * up; W rows n (gate) and up_offset + n (up); N counts gate rows
+    int dual;                  // 1: silu(gate) * up, 2: gelu_tanh(gate) * up, more: 1 + the bits of the clamped form's limit (gated_value); W rows n (gate) and up_offset + n (up); N counts gate rows
     int up_offset;
     int n_tiles, m_tiles;
 };
@@ -156,6 +156,18 @@ __device__ __forceinline__ float gate_activation(float g, int act) {
     if (act == 0) return silu(g);
     const float y = 0.7978845608028654f * (g + 0.044715f * g * g * g);
     return 0.5f * g * (2.0f - __fdividef(2.0f, 1.0f + __expf(2.0f * y)));
+}
+
+// The whole gated value.  act 0 and 1: act(gate) * up.  Any larger act is the bit pattern of a positive fp32 limit L and asks
+// for the clamped form: g = min(gate, L), u = clamp(up, -L, L), g * sigmoid(1.702 g) * (u + 1).
+__device__ __forceinline__ float gated_value(float g, float u, int act) {
+    if (act > 1) {
+        const float limit = __int_as_float(act);
+        g = fminf(g, limit);
+        u = fminf(fmaxf(u, -limit), limit);
+        return g * __fdividef(1.0f, 1.0f + __expf(-1.702f * g)) * (u + 1.0f);
+    }
+    return gate_activation(g, act) * u;
 }
 
 __global__ void __launch_bounds__(THREADS, 1)
@@ -290,7 +302,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
                     const int tok = tok0 + c + j;
                     if (tok >= p.M) break;
                     float r = __uint_as_float(raw[j]);
-                    if (p.dual) r = gate_activation(r, p.dual - 1) * __uint_as_float(raw_u[j]);
+                    if (p.dual) r = gated_value(r, __uint_as_float(raw_u[j]), p.dual - 1);
                     r += bias;
                     if (p.out_bf16) ((__nv_bfloat16*)p.out)[(size_t)tok * p.ldo + f] = __float2bfloat16_rn(r);
                     else {
@@ -354,7 +366,7 @@ MLB_EXPORT int mlb_gemm_pair(const void* x, long long ldx, const void* w, long l
                              void* out, long long ldo, int out_bf16, int accumulate, int dual, int up_offset, int M, int N,
                              int K, int stages, int sm_count, int* error_flag, cudaStream_t stream) {
     if (M < 0 || N <= 0 || K <= 0) return fail(MLB_INVALID_ARGUMENT, "gemm_pair: bad sizes M=%d N=%d K=%d", M, N, K);
-    if (dual < 0 || dual > 2) return fail(MLB_INVALID_ARGUMENT, "gemm_pair: dual must be 0, 1 (silu) or 2 (gelu_tanh)");
+    if (dual < 0) return fail(MLB_INVALID_ARGUMENT, "gemm_pair: dual must be 0, 1 (silu), 2 (gelu_tanh) or 1 + the bits of the clamped form's limit");
     if (K % 8 != 0 || ldx % 8 != 0 || ldw % 8 != 0 || ldx < K || ldw < K)
         return fail(MLB_UNSUPPORTED_SIZE, "gemm_pair: K=%d and the row pitches (%lld, %lld) must be multiples of 8 elements", K, ldx, ldw);
     if (((uintptr_t)x & 15) || ((uintptr_t)w & 15)) return fail(MLB_UNSUPPORTED_SIZE, "gemm_pair: operands must be 16-byte aligned");

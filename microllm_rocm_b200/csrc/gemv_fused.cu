@@ -108,7 +108,7 @@ struct SiluParams {
     __nv_bfloat16* out;          // [M, ldo]
     long long ldx, ldw, ldo;
     int M, I, K, up_offset, x_stride;
-    int act;                     // the gate's activation: 0 silu, 1 gelu_tanh
+    int act;                     // the gate's activation: 0 silu, 1 gelu_tanh, else the bits of the clamped form's limit (gated_value)
 };
 
 constexpr int SILU_WARPS = 4;
@@ -157,7 +157,7 @@ __global__ void __launch_bounds__(SILU_WARPS * 32) gemv_silu_kernel(SiluParams p
             gate += red[((w * 2 + 0) * NT * 4 + ne) * 32 + l2];
             up += red[((w * 2 + 1) * NT * 4 + ne) * 32 + l2];
         }
-        if (row < p.I && tok < p.M) p.out[(size_t)tok * p.ldo + row] = __float2bfloat16_rn(gate_activation(gate, p.act) * up);
+        if (row < p.I && tok < p.M) p.out[(size_t)tok * p.ldo + row] = __float2bfloat16_rn(gated_value(gate, up, p.act));
     }
 }
 
@@ -359,7 +359,7 @@ MLB_EXPORT int mlb_gemv_silu(const void* x, long long ldx, const void* w, long l
 // the same with the gate's activation chosen: act = 0 silu, 1 the tanh form of gelu
 MLB_EXPORT int mlb_gemv_gated(const void* x, long long ldx, const void* w, long long ldw, int w_rows, int up_offset, void* out,
                               long long ldo, int M, int I, int K, int act, cudaStream_t stream) {
-    if (act != 0 && act != 1) return fail(MLB_INVALID_ARGUMENT, "gemv_gated: unknown activation %d", act);
+    if (act < 0) return fail(MLB_INVALID_ARGUMENT, "gemv_gated: unknown activation %d", act);
     int status = check_operands("gemv_silu", x, ldx, w, ldw, M, K);
     if (status != MLB_OK) return status;
     if (I <= 0 || up_offset < I || up_offset + I > w_rows || ldo < I || !out)

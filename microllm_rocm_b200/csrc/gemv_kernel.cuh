@@ -41,6 +41,18 @@ __device__ __forceinline__ float gate_activation(float g, int act) {
     return 0.5f * g * (1.0f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g)));
 }
 
+// The whole gated value.  act 0 and 1: act(gate) * up.  Any larger act is the bit pattern of a positive fp32 limit L and asks
+// for the clamped form: g = min(gate, L), u = clamp(up, -L, L), g * sigmoid(1.702 g) * (u + 1).
+__device__ __forceinline__ float gated_value(float g, float u, int act) {
+    if (act > 1) {
+        const float limit = __int_as_float(act);
+        g = fminf(g, limit);
+        u = fminf(fmaxf(u, -limit), limit);
+        return g * (1.0f / (1.0f + expf(-1.702f * g))) * (u + 1.0f);
+    }
+    return gate_activation(g, act) * u;
+}
+
 struct GemvParams {
     const __nv_bfloat16* x;      // [M, ldx]
     const __nv_bfloat16* w;      // [rows, ldw]

@@ -445,6 +445,28 @@ __global__ void lightning_prepare_kernel(Columns src, int q_col, int k_col, int 
     }
 }
 
+// the same, four neighbouring columns a thread (16-byte loads and stores); HK, HV and DK are multiples of 4
+__global__ void lightning_prepare_x4_kernel(Columns src, int q_col, int k_col, int v_col, const float* __restrict__ head_decay,
+                                            float* __restrict__ q_out, float* __restrict__ k_out, float* __restrict__ v_out,
+                                            float* __restrict__ decay, long long T, int HK, int HV, int DK) {
+    pdl_prologue();
+    const int per = (2 * HK + HV) / 4;
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= T * per) return;
+    const long long t = i / per;
+    const int c = (int)(i % per) * 4;
+    auto act = [](float4 v) { return make_float4(silu_f32(v.x), silu_f32(v.y), silu_f32(v.z), silu_f32(v.w)); };
+    if (c < HK) {
+        *reinterpret_cast<float4*>(q_out + t * HK + c) = act(src.at4(t, q_col + c));
+        const float d = head_decay[c / DK];
+        *reinterpret_cast<float4*>(decay + t * HK + c) = make_float4(d, d, d, d);
+    } else if (c < 2 * HK) {
+        *reinterpret_cast<float4*>(k_out + t * HK + c - HK) = act(src.at4(t, k_col + c - HK));
+    } else {
+        *reinterpret_cast<float4*>(v_out + t * HV + c - 2 * HK) = act(src.at4(t, v_col + c - 2 * HK));
+    }
+}
+
 constexpr int ROW_THREADS = 256;
 template <typename OutT>
 __global__ void __launch_bounds__(ROW_THREADS)
@@ -476,8 +498,15 @@ MLB_EXPORT int mlb_lightning_prepare(const float* src, long long ld, int n_parti
         return fail(MLB_INVALID_ARGUMENT, "lightning_prepare: bad operands");
     if (T == 0) return MLB_OK;
     const long long n = (long long)T * (2LL * H * DK + (long long)H * DV);
-    launch_kernel(lightning_prepare_kernel, (unsigned)((n + 255) / 256), 256, 0, stream, Columns{src, ld, n_partials, partial_stride},
-                  q_col, k_col, v_col, head_decay, q_out, k_out, v_out, decay, (long long)T, H * DK, H * DV, DK);
+    const Columns cols{src, ld, n_partials, partial_stride};
+    const bool fours = DK % 4 == 0 && DV % 4 == 0 && cols.fours(q_col) && cols.fours(k_col) && cols.fours(v_col) &&
+                       ((uintptr_t)q_out | (uintptr_t)k_out | (uintptr_t)v_out | (uintptr_t)decay) % 16 == 0;
+    if (fours)
+        launch_kernel(lightning_prepare_x4_kernel, (unsigned)((n / 4 + 255) / 256), 256, 0, stream, cols, q_col, k_col, v_col, head_decay,
+                      q_out, k_out, v_out, decay, (long long)T, H * DK, H * DV, DK);
+    else
+        launch_kernel(lightning_prepare_kernel, (unsigned)((n + 255) / 256), 256, 0, stream, cols,
+                      q_col, k_col, v_col, head_decay, q_out, k_out, v_out, decay, (long long)T, H * DK, H * DV, DK);
     return check_launch("lightning_prepare");
 }
 

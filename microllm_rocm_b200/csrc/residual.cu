@@ -7,10 +7,10 @@
 //   stream_entry          x[t,:] += (x0 ? x0[t,:] : 0) + v[:]             what a pass of looped layers adds first
 //
 //   bigram_add            x[t,:] += table[row(t),:], row = (previous token * a + token * b) mod n, or row n for a sequence's
-//                         first token; the previous token of a step's first token is the sequence's state (one int per slot)
+//                         first token; the previous token of a step's first token is the sequence's state (one int per slot).
+//                         Given the token table as well, x[t,:] = tokens[id[t],:] + table[row(t),:] in one pass (bad id -> NaN).
 //   bigram_state          state[slot of a] = the last token sequence a brought in this step
 //   softcap_rows          x <- cap * tanh(x / cap) in place
-//   clamped_gate_mul      out = g * sigmoid(alpha g) * (u + 1) with g = min(gate, limit), u = clamp(up, -limit, limit)
 //
 // `s` is a per-column factor (a layer scale times the block's residual multiplier), null for none.  All sums are
 // fp32; one block per row with a fixed number of threads, so that a row's result never depends on the batch.
@@ -164,7 +164,8 @@ MLB_EXPORT int mlb_stream_entry(float* x, const float* x0, const float* v, int w
 namespace {
 
 template <typename TableT>
-__global__ void bigram_add_kernel(float* __restrict__ x, const TableT* __restrict__ table, const int* __restrict__ ids,
+__global__ void bigram_add_kernel(float* __restrict__ x, const TableT* __restrict__ table, const TableT* __restrict__ token_table, int vocab,
+                                  const int* __restrict__ ids,
                                   const int* __restrict__ token_seq, const int* __restrict__ seq_starts, const int* __restrict__ seq_pos0,
                                   const int* __restrict__ state, const int* __restrict__ slots, int num_slots, int tokens, int width,
                                   int buckets, long long mul_prev, long long mul_cur, int* __restrict__ error_flag) {
@@ -185,6 +186,16 @@ __global__ void bigram_add_kernel(float* __restrict__ x, const TableT* __restric
     const int row = prev < 0 ? buckets : (int)((prev * mul_prev + (long long)ids[t] * mul_cur) % buckets);
     const TableT* src = table + (size_t)row * width;
     float* dst = x + (size_t)t * width;
+    if (token_table) {
+        const int id = ids[t];
+        if (id < 0 || id >= vocab) {
+            for (int c = threadIdx.x; c < width; c += blockDim.x) dst[c] = nanf("");
+            return;
+        }
+        const TableT* own = token_table + (size_t)id * width;
+        for (int c = threadIdx.x; c < width; c += blockDim.x) dst[c] = to_f32(own[c]) + to_f32(src[c]);
+        return;
+    }
     for (int c = threadIdx.x; c < width; c += blockDim.x) dst[c] += to_f32(src[c]);
 }
 
@@ -203,37 +214,22 @@ __global__ void softcap_rows_kernel(float* __restrict__ x, long long n, float ca
     if (i < n) x[i] = cap * tanhf(x[i] / cap);
 }
 
-template <typename InT, typename OutT>
-__global__ void clamped_gate_mul_kernel(const InT* __restrict__ gate_up, long long ld, int n_partials, long long partial_stride,
-                                        OutT* __restrict__ out, long long rows, int width, float limit, float alpha) {
-    pdl_prologue();
-    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= rows * width) return;
-    const long long r = i / width;
-    const int c = (int)(i % width);
-    const InT* p = gate_up + r * ld + c;
-    float g = to_f32(p[0]), u = to_f32(p[width]);
-    for (int k = 1; k < n_partials; ++k) { g += to_f32(p[(size_t)k * partial_stride]); u += to_f32(p[(size_t)k * partial_stride + width]); }
-    g = fminf(g, limit);
-    u = fminf(fmaxf(u, -limit), limit);
-    const float z = alpha * g;
-    const float sg = z >= 0.0f ? 1.0f / (1.0f + expf(-z)) : expf(z) / (1.0f + expf(z));
-    out[i] = from_f32<OutT>(g * sg * (u + 1.0f));
-}
-
 }  // namespace
 
-MLB_EXPORT int mlb_bigram_add(float* x, const void* table, int table_dtype, const int* ids, const int* token_seq, const int* seq_starts,
+MLB_EXPORT int mlb_bigram_add(float* x, const void* table, int table_dtype, const void* token_table, int vocab, const int* ids, const int* token_seq, const int* seq_starts,
                               const int* seq_pos0, int* state, const int* slots, int num_slots, int tokens, int num_seqs, int width,
                               int buckets, int mul_prev, int mul_cur, int update_state, int* error_flag, cudaStream_t stream) {
     if (tokens < 0 || num_seqs < 0 || width <= 0 || buckets <= 0 || num_slots <= 0 || !x || !table || !ids || !state || !slots)
         return fail(MLB_INVALID_ARGUMENT, "bigram_add: bad operands");
     if (tokens == 0) return MLB_OK;
+    const int threads = width >= 1024 ? 256 : 128;
     if (table_dtype == MLB_BF16)
-        launch_kernel(bigram_add_kernel<__nv_bfloat16>, (unsigned)tokens, 128, 0, stream, x, (const __nv_bfloat16*)table, ids, token_seq,
+        launch_kernel(bigram_add_kernel<__nv_bfloat16>, (unsigned)tokens, threads, 0, stream, x, (const __nv_bfloat16*)table,
+                      (const __nv_bfloat16*)token_table, vocab, ids, token_seq,
                       seq_starts, seq_pos0, (const int*)state, slots, num_slots, tokens, width, buckets, (long long)mul_prev, (long long)mul_cur, error_flag);
     else if (table_dtype == MLB_F32)
-        launch_kernel(bigram_add_kernel<float>, (unsigned)tokens, 128, 0, stream, x, (const float*)table, ids, token_seq, seq_starts,
+        launch_kernel(bigram_add_kernel<float>, (unsigned)tokens, threads, 0, stream, x, (const float*)table, (const float*)token_table, vocab,
+                      ids, token_seq, seq_starts,
                       seq_pos0, (const int*)state, slots, num_slots, tokens, width, buckets, (long long)mul_prev, (long long)mul_cur, error_flag);
     else return fail(MLB_INVALID_ARGUMENT, "bigram_add: unsupported table dtype %d", table_dtype);
     if (update_state)
@@ -246,21 +242,4 @@ MLB_EXPORT int mlb_softcap_rows(float* x, long long n, float cap, cudaStream_t s
     if (n == 0) return MLB_OK;
     launch_kernel(softcap_rows_kernel, (unsigned)((n + 255) / 256), 256, 0, stream, x, n, cap);
     return check_launch("softcap_rows");
-}
-
-MLB_EXPORT int mlb_clamped_gate_mul(const void* gate_up, long long ld, int in_dtype, int n_partials, long long partial_stride, void* out,
-                                    int out_dtype, int rows, int width, float limit, float alpha, cudaStream_t stream) {
-    if (rows < 0 || width <= 0 || ld < 2LL * width || n_partials < 1 || !(limit > 0.0f)) return fail(MLB_INVALID_ARGUMENT, "clamped_gate_mul: bad sizes");
-    if (rows == 0) return MLB_OK;
-    const long long n = (long long)rows * width;
-    const unsigned blocks = (unsigned)((n + 255) / 256);
-    typedef __nv_bfloat16 bf;
-    if (in_dtype == MLB_F32 && out_dtype == MLB_F32)
-        launch_kernel(clamped_gate_mul_kernel<float, float>, blocks, 256, 0, stream, (const float*)gate_up, ld, n_partials, partial_stride, (float*)out, (long long)rows, width, limit, alpha);
-    else if (in_dtype == MLB_F32 && out_dtype == MLB_BF16)
-        launch_kernel(clamped_gate_mul_kernel<float, bf>, blocks, 256, 0, stream, (const float*)gate_up, ld, n_partials, partial_stride, (bf*)out, (long long)rows, width, limit, alpha);
-    else if (in_dtype == MLB_BF16 && out_dtype == MLB_BF16)
-        launch_kernel(clamped_gate_mul_kernel<bf, bf>, blocks, 256, 0, stream, (const bf*)gate_up, ld, n_partials, partial_stride, (bf*)out, (long long)rows, width, limit, alpha);
-    else return fail(MLB_INVALID_ARGUMENT, "clamped_gate_mul: unsupported dtype pair %d -> %d", in_dtype, out_dtype);
-    return check_launch("clamped_gate_mul");
 }

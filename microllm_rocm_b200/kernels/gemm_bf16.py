@@ -179,7 +179,7 @@ def gemv_split_partials(x: torch.Tensor, weight: torch.Tensor, bias: Optional[to
     return partial
 
 
-def gemv_silu_mul(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, activation: str = "silu") -> None:
+def gemv_silu_mul(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, activation: str = "silu", limit: Optional[float] = None) -> None:
     """out[M, I] (bf16) = act(x @ weight[:I]^T) * (x @ weight[I:2I]^T), one kernel, no partial sums; act = "silu" or
     "gelu_tanh" (`ops.ACTIVATIONS`)."""
     M, K = x.shape
@@ -188,7 +188,7 @@ def gemv_silu_mul(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, acti
         raise KernelError("gemv_silu_mul: the weight must hold gate rows then up rows, the output be bf16 [M, I]")
     L = ops.lib("gemv_fused.cu")
     build.check(L, L.mlb_gemv_gated(x.data_ptr(), x.stride(0), weight.data_ptr(), weight.stride(0), 2 * I, I, out.data_ptr(),
-                                    out.stride(0), M, I, K, ops.ACTIVATIONS[activation], ops._stream()))
+                                    out.stride(0), M, I, K, ops.activation_code(activation, limit), ops._stream()))
 
 
 def gemv_qkv_rope(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], positions: torch.Tensor,
@@ -282,7 +282,7 @@ def stream_partials(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.
 
 
 def stream_silu_mul(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, stages: int = 0,
-                    error_flag: Optional[torch.Tensor] = None, activation: str = "silu") -> None:
+                    error_flag: Optional[torch.Tensor] = None, activation: str = "silu", limit: Optional[float] = None) -> None:
     """out[M, I] (bf16) = act(x @ weight[:I]^T) * (x @ weight[I:2I]^T), the activation ("silu" or "gelu_tanh") as the
     product's epilogue."""
     M, K = x.shape
@@ -292,7 +292,7 @@ def stream_silu_mul(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, st
     flag = error_flag if error_flag is not None else device_error_flag(x.device)
     L = ops.lib("gemm_stream.cu")
     build.check(L, L.mlb_gemm_stream_gated(x.data_ptr(), x.stride(0), weight.data_ptr(), weight.stride(0), 2 * I, I,
-                                           out.data_ptr(), out.stride(0), M, I, K, int(stages), ops.ACTIVATIONS[activation],
+                                           out.data_ptr(), out.stride(0), M, I, K, int(stages), ops.activation_code(activation, limit),
                                            flag.data_ptr(), ops._stream()))
 
 
@@ -317,7 +317,7 @@ def supported(x: torch.Tensor, weight: torch.Tensor) -> bool:
 
 def gemm_pair(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, bias: Optional[torch.Tensor] = None,
               accumulate: bool = False, dual_rows: Optional[int] = None, stages: int = 0, sms: Optional[int] = None,
-              error_flag: Optional[torch.Tensor] = None, activation: str = "silu") -> None:
+              error_flag: Optional[torch.Tensor] = None, activation: str = "silu", limit: Optional[float] = None) -> None:
     """The CTA-pair tcgen05 product (`gemm_tc2.cu`) for prompt-sized token counts:
     out[M, N] = x[M, K] @ weight[:N]^T (+ bias) (+ out), or with dual_rows = I:
     out[M, I] = act(x @ weight[:I]^T) * (x @ weight[I:2I]^T), act = "silu" or "gelu_tanh"."""
@@ -336,7 +336,7 @@ def gemm_pair(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, bias: Op
     L = ops.lib("gemm_tc2.cu")
     build.check(L, L.mlb_gemm_pair(x.data_ptr(), x.stride(0), weight.data_ptr(), weight.stride(0), weight.shape[0],
                                    ops._ptr(bias), out.data_ptr(), out.stride(0), 1 if out.dtype == torch.bfloat16 else 0,
-                                   1 if accumulate else 0, 1 + ops.ACTIVATIONS[activation] if dual else 0, N if dual else 0, M, N, K, int(stages),
+                                   1 if accumulate else 0, 1 + ops.activation_code(activation, limit) if dual else 0, N if dual else 0, M, N, K, int(stages),
                                    int(sms), flag.data_ptr(), ops._stream()))
 
 

@@ -91,10 +91,9 @@ _SIGNATURES = {
                                    c_float, c_void_p],
         "mlb_add_scaled_inplace": [c_void_p, c_void_p, c_int, c_longlong, c_void_p, c_int, c_longlong, c_void_p],
         "mlb_stream_entry": [c_void_p, c_void_p, c_void_p, c_int, c_longlong, c_void_p],
-        "mlb_bigram_add": [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
-                           c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
+        "mlb_bigram_add": [c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
+                           c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
         "mlb_softcap_rows": [c_void_p, c_longlong, c_float, c_void_p],
-        "mlb_clamped_gate_mul": [c_void_p, c_longlong, c_int, c_int, c_longlong, c_void_p, c_int, c_int, c_int, c_float, c_float, c_void_p],
     },
     "layernorm.cu": {
         "mlb_layernorm": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_float, c_void_p],
@@ -264,13 +263,30 @@ def silu_mul(gate_up: torch.Tensor, out: torch.Tensor) -> None:
 
 
 ACTIVATIONS = {"silu": 0, "gelu_tanh": 1}
+CLAMPED_ACTIVATION = "clamped_swish"      # g = min(gate, L), u = clamp(up, -L, L), g * sigmoid(1.702 g) * (u + 1)
 
 
-def gated_act_mul(gate_up: torch.Tensor, out: torch.Tensor, activation: str) -> None:
-    """out[r, c] = act(gate_up[r, c]) * gate_up[r, width + c], act = "silu" or "gelu_tanh" (the tanh form of gelu);
-    the input may be [S, rows, 2*width] partial results (summed over S in order first)."""
+def activation_code(activation: str, limit: Optional[float] = None) -> int:
+    """What the gated kernels take as `act`: 0 silu, 1 gelu_tanh; for the clamped form the bit pattern of its positive fp32
+    limit (an int above 1 for every normal number), so that the limit travels in the same argument."""
+    if activation == CLAMPED_ACTIVATION:
+        import struct
+        if limit is None or not limit > 0:
+            raise KernelError("the clamped activation needs a positive limit")
+        code = struct.unpack("<i", struct.pack("<f", float(limit)))[0]
+        if code <= 1:
+            raise KernelError(f"the clamped activation's limit {limit} is not a normal fp32 number")
+        return code
     if activation not in ACTIVATIONS:
-        raise KernelError(f"gated_act_mul: unknown activation {activation!r}; known: {', '.join(ACTIVATIONS)}")
+        raise KernelError(f"unknown activation {activation!r}; known: {', '.join(ACTIVATIONS)}, {CLAMPED_ACTIVATION}")
+    return ACTIVATIONS[activation]
+
+
+def gated_act_mul(gate_up: torch.Tensor, out: torch.Tensor, activation: str, limit: Optional[float] = None) -> None:
+    """out[r, c] = act(gate_up[r, c]) * gate_up[r, width + c], act = "silu" or "gelu_tanh" (the tanh form of gelu), or the
+    clamped form with its `limit` (activation_code); the input may be [S, rows, 2*width] partial results (summed over S in
+    order first)."""
+    code = activation_code(activation, limit)
     _need(out, "out", dims=2)
     rows, width = out.shape
     n_partials, partial_stride = 1, 0
@@ -287,7 +303,7 @@ def gated_act_mul(gate_up: torch.Tensor, out: torch.Tensor, activation: str) -> 
     esz = gate_up.element_size()
     build.check(L, L.mlb_gated_act_mul(gate_up.data_ptr(), gate_up.data_ptr() + width * esz, 2 * width, dtype_tag(gate_up),
                                        n_partials, partial_stride, out.data_ptr(), dtype_tag(out), rows, width,
-                                       ACTIVATIONS[activation], _stream()))
+                                       code, _stream()))
 
 
 def cast_f32_bf16(x: torch.Tensor, out: torch.Tensor) -> None:
@@ -479,14 +495,20 @@ def stream_entry(x: torch.Tensor, x0: Optional[torch.Tensor], vector: torch.Tens
 
 
 def bigram_add(x: torch.Tensor, table: torch.Tensor, ctx, state: torch.Tensor, slots: torch.Tensor, buckets: int, mul_prev: int,
-               mul_cur: int, update_state: bool = True) -> None:
+               mul_cur: int, update_state: bool = True, token_table: Optional[torch.Tensor] = None) -> None:
     """x[t] += table[(previous token * mul_prev + token * mul_cur) mod buckets], row `buckets` for a sequence's first token.
-    The token in front of a step's first token is `state[slot]` ([slots, 1] int32), which then takes the step's last token."""
+    The token in front of a step's first token is `state[slot]` ([slots, 1] int32), which then takes the step's last token.
+    With `token_table` [vocab, width] (the dtype of `table`): x[t] = token_table[token] + that row, in one pass."""
+    if token_table is not None:
+        _need(token_table, "token_table", table.dtype, 2)
+        if token_table.shape[1] != x.shape[1]:
+            raise KernelError("bigram_add: the token table has the stream's width")
     _need(x, "x", torch.float32, 2); _need(table, "table", dims=2); _need(state, "state", torch.int32); _need(slots, "slots", torch.int32, 1)
     if table.shape != (buckets + 1, x.shape[1]) or x.shape[0] != ctx.token_ids.shape[0] or state.numel() != state.shape[0]:
         raise KernelError("bigram_add: the table has buckets + 1 rows of the stream's width, the state one int per slot")
     L = lib("residual.cu")
-    build.check(L, L.mlb_bigram_add(x.data_ptr(), table.data_ptr(), dtype_tag(table), ctx.token_ids.data_ptr(), ctx.token_seq.data_ptr(),
+    build.check(L, L.mlb_bigram_add(x.data_ptr(), table.data_ptr(), dtype_tag(table), _ptr(token_table),
+                                    token_table.shape[0] if token_table is not None else 0, ctx.token_ids.data_ptr(), ctx.token_seq.data_ptr(),
                                     ctx.seq_starts.data_ptr(), ctx.seq_pos0.data_ptr(), state.data_ptr(), slots.data_ptr(), state.shape[0],
                                     x.shape[0], ctx.num_seqs, x.shape[1], int(buckets), int(mul_prev), int(mul_cur),
                                     1 if update_state else 0, _ptr(ctx.error_flag), _stream()))
@@ -497,24 +519,6 @@ def softcap_rows(x: torch.Tensor, cap: float) -> None:
     _need(x, "x", torch.float32)
     L = lib("residual.cu")
     build.check(L, L.mlb_softcap_rows(x.data_ptr(), x.numel(), float(cap), _stream()))
-
-
-def clamped_gate_mul(gate_up: torch.Tensor, out: torch.Tensor, limit: float, alpha: float = 1.702) -> None:
-    """out[r, c] = g * sigmoid(alpha * g) * (u + 1) with g = min(gate_up[r, c], limit), u = clamp(gate_up[r, width + c], -limit,
-    limit); the input is [rows, 2 * width] or its [S, rows, 2 * width] partial results (summed over S in order first)."""
-    _need(out, "out", dims=2)
-    rows, width = out.shape
-    n_partials, partial_stride, first = 1, 0, gate_up
-    if gate_up.dim() == 3:
-        _need(gate_up, "gate_up", dims=3)
-        n_partials, partial_stride, first = gate_up.shape[0], gate_up.shape[1] * gate_up.shape[2], gate_up[0]
-    else:
-        _need(gate_up, "gate_up", dims=2)
-    if tuple(first.shape) != (rows, 2 * width):
-        raise KernelError("clamped_gate_mul: input must be [rows, 2*width]")
-    L = lib("residual.cu")
-    build.check(L, L.mlb_clamped_gate_mul(gate_up.data_ptr(), 2 * width, dtype_tag(gate_up), n_partials, partial_stride, out.data_ptr(),
-                                          dtype_tag(out), rows, width, float(limit), float(alpha), _stream()))
 
 
 # ------------------------------------------------------------------------------ small host -> device uploads

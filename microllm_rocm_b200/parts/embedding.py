@@ -60,16 +60,19 @@ class TokenEmbedding(Part):
     def forward(self, token_ids: torch.Tensor, ctx=None, state=None) -> torch.Tensor:
         """`ctx`, `state`: the step and the view of this part's per-sequence state; needed only with a pair table."""
         out = torch.empty((token_ids.shape[0], self.hidden), dtype=torch.float32, device=token_ids.device)
-        if self.scale != 1.0:
+        if self.bigram and (ctx is None or state is None):
+            raise RuntimeError("token_embedding: a pair table needs the step's context and the sequences' state")
+        one_pass = self.bigram and self.scale == 1.0 and self.bigram_table.dtype == self.table.dtype      # both rows gathered and added at once
+        if one_pass:
+            pass
+        elif self.scale != 1.0:
             ops.embed_gather_scaled(self.table, token_ids, out, self.scale)
         else:
             ops.embed_gather(self.table, token_ids, out)
         if self.bigram:
-            if ctx is None or state is None:
-                raise RuntimeError("token_embedding: a pair table needs the step's context and the sequences' state")
             b = self.bigram
             ops.bigram_add(out, self.bigram_table, ctx, state.storage, state.slots, b["buckets"], b["mul_prev"], b["mul_cur"],
-                           update_state=state.writable)
+                           update_state=state.writable, token_table=self.table if one_pass else None)
         if self.norm:
             ops.rmsnorm(out, self.norm_weight, self.norm[1], out)          # in place, fp32
         return out

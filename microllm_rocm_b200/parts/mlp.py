@@ -13,8 +13,7 @@ from ..kernels.linear import linear
 from .base import FeedForward, Runtime, StepContext, WeightSpec, register_feed_forward, scratch
 
 
-CLAMPED = "clamped_swish"
-SWISH_ALPHA = 1.702
+CLAMPED = ops.CLAMPED_ACTIVATION
 
 
 @register_feed_forward("swiglu")
@@ -41,8 +40,7 @@ class SwiGLU(FeedForward):
                 self.n_down: WeightSpec((self.hidden, self.inter))}
 
     def kernel_sources(self):
-        own = [("residual.cu", {})] if self.activation == CLAMPED else []
-        return own if self.rt.is_fp32 else own + gemm_bf16.sources(engine_only=True)
+        return [] if self.rt.is_fp32 else gemm_bf16.sources(engine_only=True)
 
     def fused_tensors(self):
         return {"gate_up_proj.weight": (WeightSpec((2 * self.inter, self.hidden)),
@@ -69,29 +67,23 @@ class SwiGLU(FeedForward):
         # boundary -- the reference's policy for its bf16 feed-forward (src/ops/optimized.cpp:676-683).
         act = scratch(ctx, "swiglu.act", (x.shape[0], self.inter), self.rt.dtype, x.device)
         flag = ctx.error_flag if ctx is not None else None      # one flag covers the step: whoever reads it sees every kernel's
-        if self.activation == CLAMPED:
-            # the products' epilogues know silu and gelu; this activation follows the product in a kernel of its own,
-            # from fp32 sums (split over K for a few tokens)
-            gate_up = linear(x, self.w_gate_up, None, torch.float32, partials_ok=True, error_flag=flag,
-                             alloc=lambda shape, dtype: scratch(ctx, "swiglu.gate_up_f32", shape, dtype, x.device))
-            ops.clamped_gate_mul(gate_up, act, self.limit, SWISH_ALPHA)
-        elif (x.dtype == torch.bfloat16 and x.shape[0] <= gemm_bf16.GEMV_SILU_MAX_TOKENS and gemm_bf16.gemv_preferred(x, self.w_gate_up)
+        if (x.dtype == torch.bfloat16 and x.shape[0] <= gemm_bf16.GEMV_SILU_MAX_TOKENS and gemm_bf16.gemv_preferred(x, self.w_gate_up)
                 and gemm_bf16.gemv_fused_supported(x, self.w_gate_up)):
             # a few tokens: one weight-streaming kernel, the activation is its epilogue
-            gemm_bf16.gemv_silu_mul(x, self.w_gate_up, act, activation=self.activation)
+            gemm_bf16.gemv_silu_mul(x, self.w_gate_up, act, activation=self.activation, limit=self.limit)
         elif x.dtype == torch.bfloat16 and gemm_bf16.gemv_preferred(x, self.w_gate_up):
             # more tokens, or a width too large for that kernel: fp32 partial sums, the activation adds them
             ops.gated_act_mul(gemm_bf16.gemv_partials(x, self.w_gate_up, alloc=lambda shape, dtype: scratch(
-                ctx, "swiglu.gate_up_partials", shape, dtype, x.device)), act, self.activation)
+                ctx, "swiglu.gate_up_partials", shape, dtype, x.device)), act, self.activation, self.limit)
         elif gemm_bf16.stream_preferred(x, self.w_gate_up):
             # up to 128 tokens: the tcgen05 weight-streaming product, the activation is its epilogue
-            gemm_bf16.stream_silu_mul(x, self.w_gate_up, act, error_flag=flag, activation=self.activation)
+            gemm_bf16.stream_silu_mul(x, self.w_gate_up, act, error_flag=flag, activation=self.activation, limit=self.limit)
         elif x.dtype == torch.bfloat16 and x.shape[0] >= gemm_bf16.PAIR_MIN_TOKENS and gemm_bf16.supported(x, self.w_gate_up):
             # a prompt portion: the CTA-pair tcgen05 product with the activation in its epilogue
-            gemm_bf16.gemm_pair(x, self.w_gate_up, act, dual_rows=self.inter, error_flag=flag, activation=self.activation)
+            gemm_bf16.gemm_pair(x, self.w_gate_up, act, dual_rows=self.inter, error_flag=flag, activation=self.activation, limit=self.limit)
         else:
             gate_up = linear(x, self.w_gate_up, None, self.rt.dtype,
                              alloc=lambda shape, dtype: scratch(ctx, "swiglu.gate_up", shape, dtype, x.device))
-            ops.gated_act_mul(gate_up, act, self.activation)
+            ops.gated_act_mul(gate_up, act, self.activation, self.limit)
         return linear(act, self.w_down, None, torch.float32, partials_ok=True, error_flag=flag,
                       alloc=lambda shape, dtype: scratch(ctx, "swiglu.out", shape, dtype, x.device))

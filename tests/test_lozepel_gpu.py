@@ -101,6 +101,7 @@ def test_pair_table_over_steps_with_slots_used_again(table_dtype):
     torch.manual_seed(2)
     buckets, a, b, W = 53, 40009, 7919, 40
     table = torch.randn(buckets + 1, W, device=DEV).to(table_dtype)
+    token_table = torch.randn(60000, W, device=DEV).to(table_dtype)
     state = torch.full((4, 1), 123456, dtype=torch.int32, device=DEV)            # slots hold a pattern: nothing of it may be read
     seqs = {0: random_tokens(9, 60000, 1), 1: random_tokens(7, 60000, 2), 2: random_tokens(4, 60000, 3)}
     want = {s: table.double()[torch.tensor(plain.bigram_rows(t, buckets, a, b))] for s, t in seqs.items()}
@@ -109,9 +110,12 @@ def test_pair_table_over_steps_with_slots_used_again(table_dtype):
     for step in plan:
         toks = [t for s, _, p, n in step for t in seqs[s][p:p + n]]
         ctx, slots = step_of([n for *_, n in step], [p for _, _, p, _ in step], [sl for _, sl, _, _ in step], toks)
+        both = torch.full((len(toks), W), float("nan"), device=DEV)                 # token row and pair row gathered and added in one pass
+        ops.bigram_add(both, table, ctx, state, slots, buckets, a, b, update_state=False, token_table=token_table)
         x = torch.zeros(len(toks), W, device=DEV)
         ops.bigram_add(x, table, ctx, state, slots, buckets, a, b)
         assert int(ctx.error_flag.item()) == 0
+        assert torch.allclose(both, x + token_table.float()[torch.tensor(toks, device=DEV)], atol=1e-6)
         at = 0
         for s, _, p, n in step:
             assert torch.allclose(x[at:at + n].double().cpu(), want[s][p:p + n].cpu(), atol=1e-6), (s, p)
@@ -307,12 +311,40 @@ def test_clamped_gate_activation(out_dtype):
     rows, width, limit = 11, 37, 1.25
     parts = torch.randn(2, rows, 2 * width, device=DEV) * 1.5                      # values on both sides of the clamp
     out = torch.empty(rows, width, dtype=out_dtype, device=DEV)
-    ops.clamped_gate_mul(parts, out, limit)
+    ops.gated_act_mul(parts, out, "clamped_swish", limit)
     x = parts.double().sum(0)
     g, u = x[:, :width].clamp(max=limit), x[:, width:].clamp(-limit, limit)
     want = g * torch.sigmoid(1.702 * g) * (u + 1)
     assert bool((x[:, :width] > limit).any()) and bool((x[:, width:] < -limit).any())
     assert torch.allclose(out.double(), want, atol=1e-5 if out_dtype == torch.float32 else 0.02)
+
+
+@pytest.mark.parametrize("tokens", [1, 8, 9, 40, 130, 300])
+def test_clamped_feed_forward_on_every_product_kernel(tokens):
+    """The dense feed-forward part alone in bf16 at token counts that take each of its routes (the few-token kernels with
+    the activation as their epilogue or behind partial sums, the streaming kernel, the library product with the activation
+    kernel, the CTA-pair kernel) against float64 on the same bf16 weights; a limit that never bites must land elsewhere."""
+    from microllm_rocm_b200.engine.loading import prepare_kernels
+    from microllm_rocm_b200.parts.base import FEED_FORWARDS, Runtime
+    torch.manual_seed(tokens)
+    hidden, inter, limit = 256, 768, 0.75
+    rt = Runtime(torch.device(DEV), torch.bfloat16)
+    w = {"gate": torch.randn(inter, hidden, device=DEV) * hidden ** -0.5, "up": torch.randn(inter, hidden, device=DEV) * hidden ** -0.5,
+         "down": torch.randn(hidden, inter, device=DEV) * inter ** -0.5}
+    w = {k: v.to(torch.bfloat16) for k, v in w.items()}
+    x = (torch.randn(tokens, hidden, device=DEV) * 1.5).to(torch.bfloat16)
+    outs = {}
+    for lim in (limit, 1e4):
+        part = FEED_FORWARDS["swiglu"](dict(hidden_size=hidden, intermediate_size=inter, names=("gate", "up", "down"),
+                                            activation="clamped_swish", limit=lim), rt)
+        prepare_kernels(SimpleNamespace(parts=lambda: [part]))
+        part.bind(dict(w))
+        y = part.forward(x, None)
+        outs[lim] = (y.sum(0) if y.dim() == 3 else y).double().cpu()
+    wd = {"m." + k: v.double().cpu() for k, v in w.items()}
+    want = plain.dense_ff({"limit": limit}, wd, "m.", x.double().cpu())
+    assert float((outs[limit] - want).abs().max() / want.abs().max()) < 0.02
+    assert float((outs[1e4] - want).abs().max() / want.abs().max()) > 0.05
 
 
 @pytest.mark.parametrize("outputs,experts,top", [(10, 7, 3), (4, 2, 4), (3, 3, 1), (40, 33, 8)])
