@@ -192,7 +192,7 @@ def attention_layer(heads, kv_heads, dim, mlp, rot_dims=None, base=10000.0, scal
                       "rot": {"base": base, "dims": rot_dims} if rot_dims else None}}
 
 
-def capped_layer(heads, kv_heads, dim, vdim, mlp, rot_dims=None, base=500000.0, scale=None, softcap=30.0, kv_from=None):
+def capped_layer(heads, kv_heads, dim, vdim, mlp, rot_dims=None, base=1000000.0, scale=None, softcap=50.0, kv_from=None):
     m = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim, "scale": scale or dim ** -0.5, "softcap": softcap,
          "rot": {"base": base, "dims": rot_dims} if rot_dims else None}
     if kv_from is not None:

@@ -67,11 +67,11 @@ CASES = {
                                attention(3, 3, 12, moe(3, 1, 36))], (11, 7, 3), None),
     # sizes the tensor-core kernels like (heads of 64); two readers of one layer's keys and values, with layers of other kinds
     # between; all of a head turned; two of a kind in a row
-    "c": model(256, 128, 2e-6, [capped(4, 2, 64, 64, moe(4, 2, 64, identity=2), rot={"base": 5e5, "dims": 64}, softcap=12.0),
+    "c": model(256, 128, 2e-6, [capped(4, 2, 64, 64, moe(4, 2, 64, identity=2), rot={"base": 2e5, "dims": 64}, softcap=12.0),
                                 attention(4, 1, 64, dense(96, 1.0), rot={"base": 1e4, "dims": 32}),
-                                capped(4, 2, 64, 64, moe(4, 2, 64, identity=2), rot={"base": 5e5, "dims": 64}, softcap=12.0, kv_from=0),
+                                capped(4, 2, 64, 64, moe(4, 2, 64, identity=2), rot={"base": 2e5, "dims": 64}, softcap=12.0, kv_from=0),
                                 parallel((4, 2, 64, 64), (2, 64, 64, (0.9, 0.999)), moe(4, 2, 64, identity=2), left_scale=0.8, right_scale=1.1),
-                                capped(4, 2, 64, 64, None, rot={"base": 5e5, "dims": 64}, softcap=12.0, kv_from=0)], (251, 17, 9), 25.0),
+                                capped(4, 2, 64, 64, None, rot={"base": 2e5, "dims": 64}, softcap=12.0, kv_from=0)], (251, 17, 9), 25.0),
     # wide heads: keys of 40 beside values of 136, an attention layer of 80; wide keys in the linear attention; no pair table
     "d": model(150, 48, 1e-6, [attention(2, 1, 80, None, rot={"base": 2000.0, "dims": 80}),
                                capped(2, 2, 40, 136, dense(24, 2.0), softcap=3.0),
